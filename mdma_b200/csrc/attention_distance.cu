@@ -3,8 +3,10 @@
 //   score(i, j) = (q_i . k_j) * scale - slope[h] * (i - j),  0 <= i - j < window (or every j <= i),
 // an ordinary softmax over the visible keys, values of a size of their own (`v_dim` may differ from
 // the key size), and optionally an output gate: the weighted sum is multiplied element by element
-// with sigmoid(gate[t, h * v_dim + d]).  No rotation is applied anywhere.  Scores, the running
-// maximum, the normaliser and the sums are float.
+// with sigmoid(gate[t, h * v_dim + d]) (or, with `gate_heads`, by sigmoid(gate[t, h]), one number per head).
+// `sinks` [heads]: a softmax with a sink: exp(sink_h) joins head h's normaliser once, with no key and no value.
+// `out_scale` multiplies the result.  No rotation is applied here.  Scores, the running maximum, the
+// normaliser and the sums are float.
 //
 // Keys and values live in pages: row (page_table[slot][p / page_size] * page_size + p % page_size) of
 // a pool [rows, kv_heads, dim] for keys and [rows, kv_heads, v_dim] for values.
@@ -49,7 +51,7 @@ attention_distance_plain_kernel(const T* __restrict__ q, int q_row_stride, const
                                 const int* __restrict__ page_table, int max_pages, int page_size,
                                 const float* __restrict__ slopes, const T* __restrict__ gate, int gate_stride,
                                 T* __restrict__ out, int n_heads, int n_kv_heads, int dim, int v_dim, int window,
-                                float scale) {
+                                float scale, const float* __restrict__ sinks, int gate_heads, float out_scale) {
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
@@ -94,15 +96,23 @@ attention_distance_plain_kernel(const T* __restrict__ q, int q_row_stride, const
         }
         m = m_new;
     }
+    if (sinks) {
+        const float sink = sinks[h];
+        const float m_new = fmaxf(m, sink);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sink - m_new);
+#pragma unroll
+        for (int j = 0; j < kMaxDim / 32; ++j) acc[j] *= corr;
+    }
     T* op = out + ((size_t)t * n_heads + h) * v_dim;
-    const T* gp = gate ? gate + (size_t)t * gate_stride + (size_t)h * v_dim : nullptr;
-    const float inv = 1.0f / l;
+    const T* gp = gate ? gate + (size_t)t * gate_stride + (gate_heads ? (size_t)h : (size_t)h * v_dim) : nullptr;
+    const float inv = out_scale / l;
 #pragma unroll
     for (int j = 0; j < kMaxDim / 32; ++j) {
         const int d = lane + 32 * j;
         if (d < v_dim) {
             float o = acc[j] * inv;
-            if (gp) o *= 1.0f / (1.0f + expf(-to_float(gp[d])));
+            if (gp) o *= 1.0f / (1.0f + expf(-to_float(gp[gate_heads ? 0 : d])));
             op[d] = from_float<T>(o);
         }
     }
@@ -144,7 +154,7 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
                                 const int* __restrict__ page_table, int max_pages, int page_size,
                                 const float* __restrict__ slopes, const T* __restrict__ gate, int gate_stride,
                                 T* __restrict__ out, int n_heads, int n_kv_heads, int dim, int v_dim, int window,
-                                float scale) {
+                                float scale, const float* __restrict__ sinks, int gate_heads, float out_scale) {
     chain_release();
     chain_wait();
     extern __shared__ float smem[];
@@ -301,8 +311,14 @@ attention_distance_tiled_kernel(const T* __restrict__ q, int q_row_stride, const
         const int r = pr / group, g = pr % group;
         const int h = kvh * group + g;
         const size_t t = (size_t)(t0 + r0 + r);
-        float o = so[e] / sl[pr];
-        if (gate) o *= 1.0f / (1.0f + expf(-to_float(gate[t * gate_stride + (size_t)h * v_dim + d])));
+        float o = so[e], l = sl[pr];
+        if (sinks) {
+            const float sink = sinks[h], m = sm[pr];
+            if (sink > m) { const float c = expf(m - sink); o *= c; l = l * c + 1.0f; }
+            else l += expf(sink - m);
+        }
+        o = o / l * out_scale;
+        if (gate) o *= 1.0f / (1.0f + expf(-to_float(gate[t * gate_stride + (gate_heads ? (size_t)h : (size_t)h * v_dim + d)])));
         out[(t * n_heads + h) * v_dim + d] = from_float<T>(o);
     }
 }
@@ -344,7 +360,7 @@ int mdma_attention_distance(const void* q, int dtype, int q_row_stride, const vo
                             const int* seq_pos0, const int* page_table, int max_pages, int page_size,
                             const float* slopes, const void* gate, int gate_stride, void* out, int n_tokens, int n_seqs,
                             int max_new, int n_heads, int n_kv_heads, int dim, int v_dim, int window, float scale,
-                            int tiled, cudaStream_t stream) {
+                            int tiled, const float* sinks, int gate_heads, float out_scale, cudaStream_t stream) {
     MDMA_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention: %d heads over %d kv heads", n_heads, n_kv_heads);
     MDMA_REQUIRE(dim > 0 && dim <= kMaxDim && v_dim > 0 && v_dim <= kMaxDim, "attention: head sizes %d / %d are beyond the limit %d", dim, v_dim, kMaxDim);
     MDMA_REQUIRE(page_table && page_size > 0 && max_pages > 0 && window >= 0, "attention: bad cache geometry");
@@ -367,7 +383,7 @@ int mdma_attention_distance(const void* q, int dtype, int q_row_stride, const vo
             launch_chained(attention_distance_tiled_kernel<T, GH>, grid, dim3(kTileWarps * 32), smem, stream, (const T*)q,  \
                            q_row_stride, (const T*)k_cache, (const T*)v_cache, seq_start, seq_pos0, seq_slot, page_table,   \
                            max_pages, page_size, slopes, (const T*)gate, gate_stride, (T*)out, n_heads, n_kv_heads, dim,    \
-                           v_dim, window, scale);                                                                           \
+                           v_dim, window, scale, sinks, gate_heads, out_scale);                                             \
         } while (0)
         MDMA_DISPATCH_DTYPE(dtype, T, {
             if (together) MDMA_TILED_LAUNCH(kHeadsTogether);
@@ -381,7 +397,8 @@ int mdma_attention_distance(const void* q, int dtype, int q_row_stride, const vo
     MDMA_DISPATCH_DTYPE(dtype, T,
         launch_chained(attention_distance_plain_kernel<T>, grid, dim3(128), 0, stream, (const T*)q, q_row_stride,
                        (const T*)k_cache, (const T*)v_cache, tok_seq, tok_pos, seq_slot, page_table, max_pages, page_size,
-                       slopes, (const T*)gate, gate_stride, (T*)out, n_heads, n_kv_heads, dim, v_dim, window, scale));
+                       slopes, (const T*)gate, gate_stride, (T*)out, n_heads, n_kv_heads, dim, v_dim, window, scale,
+                       sinks, gate_heads, out_scale));
     MDMA_LAUNCH_OK("attention_distance");
     return 0;
 }

@@ -27,7 +27,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 LIBRARIES = {
     # name: (sources, headers, link flags)
     "core": (["elementwise.cu", "gemm_simt.cu", "attention_simple.cu", "sampling.cu", "sequence_mix.cu",
-             "latent_attention.cu", "rglru.cu", "attention_distance.cu", "routed_ffn.cu"], ["common.cuh"], []),
+             "latent_attention.cu", "rglru.cu", "attention_distance.cu", "routed_ffn.cu", "attention_prepare.cu",
+             "linear_attention.cu"], ["common.cuh"], []),
     "tensor": (["gemm_tcgen05.cu", "attention_mma.cu", "attention_tc.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh"], []),
     "noalloc": (["attention_noalloc.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh", "attention_noalloc.h"], []),
 }

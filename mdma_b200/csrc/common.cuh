@@ -28,13 +28,15 @@ static inline int fail(const char* fmt, ...) {
 }
 // What a matrix product adds on its way out: a vector over the output features (for the second matrix of
 // a gated product too), kept as float32 or bfloat16, and which activation a gated product applies to its gate.
-enum Activation : int { kActSilu = 0, kActGeluTanh = 1 };
+enum Activation : int { kActSilu = 0, kActGeluTanh = 1, kActGeluErf = 2, kActSwishLimit = 3 };
 struct Ending {
     const void* bias;     // [n_features] or null
     const void* bias2;    // the second matrix's, or null
     int bias_dtype;       // DType of both
     int act;              // Activation of a gated product's gate, or of a stored product when `store_act` is set
     int store_act;        // a product that is stored: out = act(sum + bias) (a feed-forward without a gate)
+    float act_limit;      // kActSwishLimit: the gate is cut off above `limit`, the other product outside +-limit
+    float act_alpha;      // kActSwishLimit: the sigmoid's slope
 };
 __device__ __forceinline__ float ending_bias(const void* b, int dtype, int f) {
     if (b == nullptr) return 0.f;
@@ -43,12 +45,32 @@ __device__ __forceinline__ float ending_bias(const void* b, int dtype, int f) {
 // act(g) of a gated feed-forward in plain float arithmetic (the 32-bit engine) ...
 __device__ __forceinline__ float gate_activation(float g, int act) {
     if (act == kActGeluTanh) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    if (act == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
     return g / (1.0f + expf(-g));
 }
 // ... and with the fast exponential (the bfloat16 engine): 0.5 (1 + tanh t) = 1 / (1 + e^(-2t)).
 __device__ __forceinline__ float gate_activation_fast(float g, int act) {
     if (act == kActGeluTanh) return g / (1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+    if (act == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
     return g / (1.0f + __expf(-g));
+}
+// What a gated feed-forward makes of its two products g and u: act(g) * u, or, for kActSwishLimit,
+// g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit) and u' = u kept within +-limit.
+__device__ __forceinline__ float gated_pair(float g, float u, int act, float limit, float alpha) {
+    if (act == kActSwishLimit) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    return gate_activation(g, act) * u;
+}
+__device__ __forceinline__ float gated_pair_fast(float g, float u, int act, float limit, float alpha) {
+    if (act == kActSwishLimit) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + __expf(-alpha * g)) * (u + 1.0f);
+    }
+    return gate_activation_fast(g, act) * u;
 }
 
 #define MDMA_REQUIRE(cond, ...) \

@@ -100,7 +100,7 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
             } else if (MODE == kStoreAct) {
                 *o = from_float<TO>(gate_activation(r, e.act));
             } else {
-                *o = from_float<TO>(gate_activation(r, e.act) * (acc2[i][j] + ending_bias(e.bias2, e.bias_dtype, n)));
+                *o = from_float<TO>(gated_pair(r, acc2[i][j] + ending_bias(e.bias2, e.bias_dtype, n), e.act, e.act_limit, e.act_alpha));
             }
         }
     }
@@ -131,15 +131,17 @@ using namespace mdma;
 
 extern "C" int mdma_gemm_simt(int mode, const void* A, int a_dtype, int lda, const void* W, const void* W2,
                               int w_dtype, void* out, int out_dtype, int ldo, int M, int N, int K,
-                              const void* bias, const void* bias2, int bias_dtype, int act, cudaStream_t stream) {
+                              const void* bias, const void* bias2, int bias_dtype, int act, float act_limit, float act_alpha,
+                              cudaStream_t stream) {
     MDMA_REQUIRE(M >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm_simt: bad sizes M=%d N=%d K=%d lda=%d ldo=%d", M, N, K, lda, ldo);
     MDMA_REQUIRE(mode != kSwiGLU || W2 != nullptr, "gemm_simt: SwiGLU needs two weights");
     MDMA_REQUIRE(mode != kAccumulate || out_dtype == kF32, "gemm_simt: the residual stream is float");
     MDMA_REQUIRE((size_t)((M + TM - 1) / TM) <= 65535, "gemm_simt: too many rows (%d)", M);
-    MDMA_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_simt: unknown activation %d", act);
+    MDMA_REQUIRE(act >= kActSilu && act <= kActSwishLimit, "gemm_simt: unknown activation %d", act);
+    MDMA_REQUIRE(act != kActSwishLimit || mode == kSwiGLU, "gemm_simt: the limited activation belongs to a gated product");
     MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_simt: unknown bias dtype %d", bias_dtype);
     if (M == 0) return 0;
-    const Ending e{bias, mode == kSwiGLU ? bias2 : nullptr, bias_dtype, act};
+    const Ending e{bias, mode == kSwiGLU ? bias2 : nullptr, bias_dtype, act, 0, act_limit, act_alpha};
     if (a_dtype == kF32 && w_dtype == kF32 && out_dtype == kF32)
         return launch_gemm<float, float, float>(mode, A, lda, W, W2, out, ldo, M, N, K, e, stream);
     if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kBF16)

@@ -252,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         if (j >= valid) break;
                         const int t = t0 + c + j;
                         float r = v[j] + b1;
-                        if (MODE == kTcSwiGLU) r = gate_activation_fast(r, p.ending.act) * (u[j] + b2);
+                        if (MODE == kTcSwiGLU) r = gated_pair_fast(r, u[j] + b2, p.ending.act, p.ending.act_limit, p.ending.act_alpha);
                         if (MODE == kTcStore && p.ending.store_act) r = gate_activation_fast(r, p.ending.act);
                         if (MODE == kTcPartial) {
                             p.partial[((size_t)blockIdx.z * p.n_tokens + t) * p.n_features + f] = r;
@@ -529,7 +529,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                             if (q >= valid) break;
                             const int t = t0 + c + q;
                             float r = v[q] + b1;
-                            if (MODE == kTcSwiGLU) r = gate_activation_fast(r, p.ending.act) * (u[q] + b2);
+                            if (MODE == kTcSwiGLU) r = gated_pair_fast(r, u[q] + b2, p.ending.act, p.ending.act_limit, p.ending.act_alpha);
                             if (MODE == kTcStore && p.ending.store_act) r = gate_activation_fast(r, p.ending.act);
                             if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
                             else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
@@ -905,7 +905,8 @@ int mdma_splitk_reduce(int mode, const float* partial, int splits, int n_tokens,
 int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2, void* out, int out_f32,
                  int ldo, int n_tokens, int n_features, int K, int bn, int splits, float* scratch,
                  long scratch_floats, int* status, int defer_reduce, int* splits_used, int* sk_flags,
-                 const void* bias, const void* bias2, int bias_dtype, int act, cudaStream_t stream) {
+                 const void* bias, const void* bias2, int bias_dtype, int act, float act_limit, float act_alpha,
+                 cudaStream_t stream) {
     if (splits_used) *splits_used = 1;
     // bit 8 of `act`: the product is stored with the activation applied, out = act(a W^T + b)
     const int store_act = (act >> 8) & 1;
@@ -917,9 +918,10 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!w2 || ((uintptr_t)w2 & 15) == 0),
                  "gemm_tc: operands must be 16-byte aligned");
     MDMA_REQUIRE(mode != kTcSwiGLU || w2, "gemm_tc: SwiGLU needs two weights");
-    MDMA_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tc: unknown activation %d", act);
+    MDMA_REQUIRE(act >= kActSilu && act <= kActSwishLimit, "gemm_tc: unknown activation %d", act);
+    MDMA_REQUIRE(act != kActSwishLimit || mode == kTcSwiGLU, "gemm_tc: the limited activation belongs to a gated product");
     MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_tc: unknown bias dtype %d", bias_dtype);
-    const Ending ending{bias, mode == kTcSwiGLU ? bias2 : nullptr, bias_dtype, act, store_act};
+    const Ending ending{bias, mode == kTcSwiGLU ? bias2 : nullptr, bias_dtype, act, store_act, act_limit, act_alpha};
     MDMA_REQUIRE(mode != kTcAccumulate || out_f32, "gemm_tc: the residual stream is float");
     MDMA_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: unknown mode %d", mode);
     MDMA_REQUIRE(bn == 512 || (n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
@@ -1007,7 +1009,8 @@ static RunStreams* run_streams() {
 
 int mdma_gemm_tc_runs(int mode, const void* x, int ldx, const void* w, const void* w2, long w_stride, void* out,
                       int out_f32, int ldo, const int* first, int n_runs, int n_features, int K, int sm_count,
-                      float* scratch, long scratch_floats, int* status, int* sk_flags, int act, cudaStream_t stream) {
+                      float* scratch, long scratch_floats, int* status, int* sk_flags, int act, float act_limit,
+                      float act_alpha, cudaStream_t stream) {
     (void)scratch; (void)scratch_floats; (void)sk_flags;
     MDMA_REQUIRE(n_runs >= 0 && first != nullptr && w_stride >= (long)n_features * K, "gemm_tc_runs: bad run list");
     MDMA_REQUIRE(mode == kTcStore || mode == kTcSwiGLU, "gemm_tc_runs: stored and gated products only");
@@ -1034,7 +1037,7 @@ int mdma_gemm_tc_runs(int mode, const void* x, int ldx, const void* w, const voi
         const char* w2r = w2 ? (const char*)w2 + (size_t)r * w_stride * 2 : nullptr;
         char* outr = (char*)out + (size_t)lo * ldo * out_bytes;
         rc = mdma_gemm_tc(mode, xr, ldx, wr, w2r, outr, out_f32, ldo, m, n_features, K, bn, splits, nullptr, 0, status, 0,
-                          nullptr, nullptr, nullptr, nullptr, kF32, act, rs->side[at % lanes]);
+                          nullptr, nullptr, nullptr, nullptr, kF32, act, act_limit, act_alpha, rs->side[at % lanes]);
         ++at;
     }
     for (int i = 0; i < lanes; ++i) {        // joined also after an error: nothing is left running beside the stream

@@ -2,15 +2,17 @@
 //
 // Router (one block per token, float arithmetic):
 //     z = R h                              logits over all routed outputs (experts, then identity experts)
-//     s = softmax(z)
+//     s = softmax(z), or sigmoid(z) element by element (`scoring` 1)
 //     c = s + correction                   choice scores
-//     experts form `n_groups` equal groups of neighbours; a group's score is its largest c; only the
-//     `keep_groups` best groups stay eligible (the others count as minus infinity)
+//     experts form `n_groups` equal groups of neighbours; a group's score is the sum of its `group_top`
+//     largest c (1: its largest); only the `keep_groups` best groups stay eligible (the others count as
+//     minus infinity)
 //     the `top` eligible experts with the largest c are chosen (ties: the lower number)
-//     weight_j = s[chosen_j] / (sum of the chosen s + 1e-20)
+//     weight_j = s[chosen_j] / (sum of the chosen s + 1e-20), or s[chosen_j] itself (`renormalize` 0)
 // and, if the layer has a shared expert with a gate, sg = sigmoid(g . h), one number per token.
 //
-// Experts: expert e maps h to D_e (act(G_e h) * (U_e h)), act = SiLU; the last `n_identity` routed
+// Experts: expert e maps h to D_e pair(G_e h, U_e h), pair(g, u) = SiLU(g) * u or another gated form of
+// `gated_pair`; the last `n_identity` routed
 // outputs have no matrices, their output is h itself.  The matrices of all experts are stacked:
 // G and U [experts * ff, width], D [experts * width, ff].
 //
@@ -23,7 +25,7 @@
 
 namespace mdma {
 
-constexpr int kMaxRouted = 1024, kMaxTop = 32;
+constexpr int kMaxRouted = 1024, kMaxTop = 32, kMaxGroupTop = 8;
 
 // eight consecutive elements as floats, by 16-byte loads (the address must be 16-byte aligned)
 __device__ __forceinline__ void load8(const float* p, float* v) {
@@ -64,6 +66,7 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 route_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ router, const TC* __restrict__ correction,
              const TW* __restrict__ shared_gate, int width, int n_routed, int top, int n_groups, int keep_groups,
+             int scoring, int group_top, int renormalize,
              int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_scale) {
     chain_release();
     chain_wait();
@@ -83,14 +86,16 @@ route_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ rout
     __syncthreads();
     if (threadIdx.x != 0) return;
     // the rest is a few hundred operations: one thread, one order
-    float m = -INFINITY;
-    for (int e = 0; e < n_routed; ++e) m = fmaxf(m, z[e]);
-    float sum = 0.f;
-    for (int e = 0; e < n_routed; ++e) { z[e] = expf(z[e] - m); sum += z[e]; }
-    for (int e = 0; e < n_routed; ++e) {
-        z[e] = z[e] / sum;                                            // s
-        c[e] = z[e] + (correction ? to_float(correction[e]) : 0.f);   // choice score
+    if (scoring == 1) {
+        for (int e = 0; e < n_routed; ++e) z[e] = 1.0f / (1.0f + expf(-z[e]));
+    } else {
+        float m = -INFINITY;
+        for (int e = 0; e < n_routed; ++e) m = fmaxf(m, z[e]);
+        float sum = 0.f;
+        for (int e = 0; e < n_routed; ++e) { z[e] = expf(z[e] - m); sum += z[e]; }
+        for (int e = 0; e < n_routed; ++e) z[e] = z[e] / sum;
     }
+    for (int e = 0; e < n_routed; ++e) c[e] = z[e] + (correction ? to_float(correction[e]) : 0.f);   // z: s; c: choice score
     if (n_groups > 1 && keep_groups < n_groups) {
         const int per = n_routed / n_groups;
         // the best group not yet kept is looked for keep_groups times (ties: the lower number); a bit per group
@@ -102,7 +107,21 @@ route_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ rout
             for (int g = 0; g < n_groups; ++g) {
                 if (kept[g >> 5] >> (g & 31) & 1u) continue;
                 float gs = -INFINITY;
-                for (int e = g * per; e < (g + 1) * per; ++e) gs = fmaxf(gs, c[e]);
+                if (group_top <= 1) {
+                    for (int e = g * per; e < (g + 1) * per; ++e) gs = fmaxf(gs, c[e]);
+                } else {
+                    // the group's largest scores, largest first, are added up (a group of fewer members: all of them)
+                    float best_of[kMaxGroupTop];
+                    const int n_best = min(group_top, per);
+                    for (int i = 0; i < n_best; ++i) best_of[i] = -INFINITY;
+                    for (int e = g * per; e < (g + 1) * per; ++e) {
+                        float v = c[e];
+                        for (int i = 0; i < n_best; ++i)
+                            if (v > best_of[i]) { const float tmp = best_of[i]; best_of[i] = v; v = tmp; }
+                    }
+                    gs = 0.f;
+                    for (int i = 0; i < n_best; ++i) gs += best_of[i];
+                }
                 if (best < 0 || gs > best_score) { best = g; best_score = gs; }
             }
             if (best >= 0) kept[best >> 5] |= 1u << (best & 31);
@@ -123,7 +142,7 @@ route_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ rout
     }
     for (int k = 0; k < top; ++k) {
         chosen[(size_t)t * top + k] = pick[k];
-        weights[(size_t)t * top + k] = pick[k] >= 0 ? z[pick[k]] / (total + 1e-20f) : 0.f;
+        weights[(size_t)t * top + k] = pick[k] < 0 ? 0.f : renormalize ? z[pick[k]] / (total + 1e-20f) : z[pick[k]];
     }
 }
 
@@ -132,7 +151,8 @@ route_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ rout
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
 expert_gate_up_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ G, const TW* __restrict__ U,
-                      const int* __restrict__ chosen, int n_experts, int top, int width, int ff, TA* __restrict__ act) {
+                      const int* __restrict__ chosen, int n_experts, int top, int width, int ff, TA* __restrict__ act,
+                      int pair_act, float act_limit, float act_alpha) {
     chain_release();
     chain_wait();
     extern __shared__ float hs[];
@@ -166,7 +186,7 @@ expert_gate_up_kernel(const TA* __restrict__ h, int h_stride, const TW* __restri
         }
         ag = warp_sum(ag);
         au = warp_sum(au);
-        if (lane == 0) act[(size_t)pair * ff + f] = from_float<TA>(ag / (1.0f + expf(-ag)) * au);
+        if (lane == 0) act[(size_t)pair * ff + f] = from_float<TA>(gated_pair(ag, au, pair_act, act_limit, act_alpha));
     }
 }
 
@@ -269,7 +289,7 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
 expert_gate_up_sorted_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ G, const TW* __restrict__ U,
                              const int* __restrict__ first, const int* __restrict__ order, int top, int width, int ff,
-                             TA* __restrict__ act) {
+                             TA* __restrict__ act, int pair_act, float act_limit, float act_alpha) {
     chain_release();
     chain_wait();
     const int e = blockIdx.z;
@@ -326,7 +346,7 @@ expert_gate_up_sorted_kernel(const TA* __restrict__ h, int h_stride, const TW* _
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int f = f0 + fx * 4 + j;
-            if (f < ff) act[(size_t)pr * ff + f] = from_float<TA>(ag[i][j] / (1.0f + expf(-ag[i][j])) * au[i][j]);
+            if (f < ff) act[(size_t)pr * ff + f] = from_float<TA>(gated_pair(ag[i][j], au[i][j], pair_act, act_limit, act_alpha));
         }
     }
 }
@@ -426,7 +446,10 @@ extern "C" {
 
 int mdma_route(const void* h, int h_dtype, int h_stride, const void* router, int w_dtype, const void* correction,
                int c_dtype, const void* shared_gate, int n_tokens, int width, int n_routed, int top, int n_groups,
-               int keep_groups, int* chosen, float* weights, float* shared_scale, cudaStream_t stream) {
+               int keep_groups, int scoring, int group_top, int renormalize, int* chosen, float* weights,
+               float* shared_scale, cudaStream_t stream) {
+    MDMA_REQUIRE(scoring >= 0 && scoring <= 1 && group_top >= 1 && group_top <= kMaxGroupTop,
+                 "route: scoring %d, a group's score over its %d largest (at most %d)", scoring, group_top, kMaxGroupTop);
     MDMA_REQUIRE(n_tokens >= 0 && width > 0, "route: bad sizes");
     MDMA_REQUIRE(n_routed > 0 && n_routed <= kMaxRouted, "route: %d routed outputs, the kernel takes up to %d", n_routed, kMaxRouted);
     MDMA_REQUIRE(top > 0 && top <= kMaxTop && top <= n_routed, "route: top %d of %d (at most %d)", top, n_routed, kMaxTop);
@@ -438,7 +461,7 @@ int mdma_route(const void* h, int h_dtype, int h_stride, const void* router, int
         MDMA_DISPATCH_DTYPE(c_dtype, TC,
             launch_chained(route_kernel<TA, TW, TC>, dim3(n_tokens), dim3(256), 0, stream, (const TA*)h, h_stride,
                            (const TW*)router, (const TC*)correction, (const TW*)shared_gate, width, n_routed, top,
-                           n_groups, keep_groups, chosen, weights, shared_scale)));
+                           n_groups, keep_groups, scoring, group_top, renormalize, chosen, weights, shared_scale)));
     MDMA_LAUNCH_OK("route");
     return 0;
 }
@@ -446,7 +469,8 @@ int mdma_route(const void* h, int h_dtype, int h_stride, const void* router, int
 // Token by token: act [n_tokens * top, ff] in h's dtype is scratch; x [n_tokens, width] float takes the sum.
 int mdma_experts_by_token(const void* h, int h_dtype, int h_stride, const void* G, const void* U, const void* D,
                           int w_dtype, const int* chosen, const float* weights, int n_tokens, int n_experts, int top,
-                          int width, int ff, void* act, float* x, cudaStream_t stream) {
+                          int width, int ff, void* act, float* x, int pair_act, float act_limit, float act_alpha,
+                          cudaStream_t stream) {
     MDMA_REQUIRE(n_tokens >= 0 && width > 0 && ff > 0 && top > 0 && n_experts >= 0, "experts: bad sizes");
     MDMA_REQUIRE((size_t)width * sizeof(float) <= 160 * 1024, "experts: width %d is beyond the kernel's shared memory", width);
     if (n_tokens == 0) return 0;
@@ -461,7 +485,7 @@ int mdma_experts_by_token(const void* h, int h_dtype, int h_stride, const void* 
             }
             launch_chained(expert_gate_up_kernel<TA, TW>, dim3(n_tokens * top, fparts), dim3(256),
                            (size_t)width * sizeof(float), stream, (const TA*)h, h_stride, (const TW*)G, (const TW*)U, chosen,
-                           n_experts, top, width, ff, (TA*)act);
+                           n_experts, top, width, ff, (TA*)act, pair_act, act_limit, act_alpha);
         }
         launch_chained(expert_down_kernel<TA, TW>, dim3(n_tokens, wparts), dim3(256), 0, stream, (const TA*)act, (const TA*)h,
                        h_stride, (const TW*)D, chosen, weights, n_experts, top, width, ff, x);
@@ -474,7 +498,8 @@ int mdma_experts_by_token(const void* h, int h_dtype, int h_stride, const void* 
 // y [n_tokens * top, width] floats are scratch.
 int mdma_experts_sorted(const void* h, int h_dtype, int h_stride, const void* G, const void* U, const void* D,
                         int w_dtype, const int* chosen, const float* weights, int n_tokens, int n_experts, int top,
-                        int width, int ff, int* first, int* order, void* act, float* y, float* x, cudaStream_t stream) {
+                        int width, int ff, int* first, int* order, void* act, float* y, float* x, int pair_act,
+                        float act_limit, float act_alpha, cudaStream_t stream) {
     MDMA_REQUIRE(n_tokens >= 0 && width > 0 && ff > 0 && top > 0 && n_experts >= 0 && n_experts <= kMaxRouted, "experts: bad sizes");
     if (n_tokens == 0) return 0;
     const int n_pairs = n_tokens * top;
@@ -486,7 +511,7 @@ int mdma_experts_sorted(const void* h, int h_dtype, int h_stride, const void* G,
             if (int rc = sort_pairs(chosen, n_pairs, n_experts, first, order, nullptr, stream)) return rc;
             launch_chained(expert_gate_up_sorted_kernel<TA, TW>, dim3((ff + kFeatTile - 1) / kFeatTile, pair_tiles, n_experts),
                            dim3(256), 0, stream, (const TA*)h, h_stride, (const TW*)G, (const TW*)U, first, order, top, width,
-                           ff, (TA*)act);
+                           ff, (TA*)act, pair_act, act_limit, act_alpha);
             launch_chained(expert_down_sorted_kernel<TA, TW>, dim3((width + kFeatTile - 1) / kFeatTile, pair_tiles, n_experts),
                            dim3(256), 0, stream, (const TA*)act, (const TW*)D, first, order, width, ff, y);
         }

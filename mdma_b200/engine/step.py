@@ -112,7 +112,9 @@ def lay_out(model: DecoderModel, carver: Carver, *, dtype, device, sms: int, max
     shapes = []
     for b in model.blocks:
         m = b.mixer
-        if all(hasattr(m, a) for a in ("n_heads", "n_kv_heads", "head_dim")):
+        if hasattr(m, "attention_shapes"):          # a mixer made of several
+            shapes.extend(m.attention_shapes())
+        elif all(hasattr(m, a) for a in ("n_heads", "n_kv_heads", "head_dim")):
             shapes.append((m.n_heads, m.n_kv_heads, m.head_dim))
     floats = 0
     if dtype == torch.bfloat16:

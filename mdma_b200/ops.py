@@ -104,23 +104,28 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
           ctypes.c_long(split_stride), _stream())
 
 
-ACT_SILU, ACT_GELU_TANH = 0, 1
-ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+ACT_SILU, ACT_GELU_TANH, ACT_GELU, ACT_SWISH_LIMIT = 0, 1, 2, 3
+# "gelu" is the exact one, 0.5 z (1 + erf(z / sqrt 2)).  "swish_limit" belongs to gated products only: with the gate's
+# product g cut off above `limit` and the other product u kept within +-limit, g sigmoid(alpha g) (u + 1).
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU, "swish_limit": ACT_SWISH_LIMIT}
 
 
-def ending_args(n_features: int, bias: Optional[torch.Tensor], bias2: Optional[torch.Tensor], act: int):
-    """The four arguments by which the product kernels take their bias vectors and the gate's activation."""
+def ending_args(n_features: int, bias: Optional[torch.Tensor], bias2: Optional[torch.Tensor], act: int,
+                act_limit: float = 0.0, act_alpha: float = 1.0):
+    """The arguments by which the product kernels take their bias vectors, the gate's activation and its constants."""
     for b in (bias, bias2):
         if b is not None:
             assert b.is_cuda and b.is_contiguous() and b.shape == (n_features,)
             assert bias.dtype == b.dtype and b.dtype in (torch.float32, torch.bfloat16)
     assert bias2 is None or bias is not None
-    return _ptr(bias), _ptr(bias2), _i(dtype_code(bias.dtype) if bias is not None else F32), _i(act)
+    return (_ptr(bias), _ptr(bias2), _i(dtype_code(bias.dtype) if bias is not None else F32), _i(act), _f(act_limit),
+            _f(act_alpha))
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = GEMM_STORE,
               w2: Optional[torch.Tensor] = None, m: Optional[int] = None, bias: Optional[torch.Tensor] = None,
-              bias2: Optional[torch.Tensor] = None, act: int = ACT_SILU) -> None:
+              bias2: Optional[torch.Tensor] = None, act: int = ACT_SILU, act_limit: float = 0.0,
+              act_alpha: float = 1.0) -> None:
     """out[:m] (=, +=) a[:m] @ w.T (+ bias) on the CUDA cores; the gated mode takes gate=w, up=w2 and
     gives act(gate) * up."""
     _need_cuda(a, w, out, w2)
@@ -133,7 +138,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = G
         assert w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous()
     _call("core", "mdma_gemm_simt", _i(mode), _ptr(a), _i(dtype_code(a.dtype)), _i(a.stride(0)),
           _ptr(w), _ptr(w2), _i(dtype_code(w.dtype)), _ptr(out), _i(dtype_code(out.dtype)),
-          _i(out.stride(0)), _i(M), _i(N), _i(K), *ending_args(N, bias, bias2, act), _stream())
+          _i(out.stride(0)), _i(M), _i(N), _i(K), *ending_args(N, bias, bias2, act, act_limit, act_alpha), _stream())
 
 
 def rope_cache_write(qkv: torch.Tensor, n_tokens: int, tok_seq, tok_pos, seq_slot, inv_freq,
@@ -520,27 +525,33 @@ def attention_distance_tiled_fits(n_heads: int, n_kv_heads: int, dim: int, v_dim
 
 def attention_distance(q, k_cache, v_cache, ctx, page_table, max_pages: int, page_size: int, slopes, gate, out,
                        n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int, scale: float,
-                       tiled: bool = False) -> None:
+                       tiled: bool = False, sinks=None, gate_heads: bool = False, out_scale: float = 1.0) -> None:
     """Softmax attention with score (q.k) * scale - slopes[h] * distance over the paged cache; q: rows whose first
     n_heads * dim columns are the queries; `gate` (rows of n_heads * v_dim, optional): the result is multiplied by
-    its sigmoid; out [T, n_heads * v_dim].  `tiled`: the kernel that stages keys and values per tile of query rows."""
+    its sigmoid; out [T, n_heads * v_dim].  `tiled`: the kernel that stages keys and values per tile of query rows.
+    `sinks` [n_heads] floats: exp(sink) joins each head's normaliser once; `gate_heads`: the gate has one number per
+    head (rows of n_heads); `out_scale` multiplies the result."""
     _need_cuda(q, k_cache, v_cache, page_table, slopes, gate, out)
     assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == k_cache.dtype == v_cache.dtype
     assert out.shape[1] == n_heads * v_dim and out.shape[0] >= ctx.n_tokens
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == n_heads and slopes.is_contiguous())
-    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_heads * v_dim)
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] >= (n_heads if gate_heads else n_heads * v_dim))
+    assert sinks is None or (sinks.is_cuda and sinks.dtype == torch.float32 and sinks.numel() == n_heads and sinks.is_contiguous())
     _call("core", "mdma_attention_distance", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(k_cache), _ptr(v_cache),
           _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0),
           _ptr(page_table), _i(max_pages), _i(page_size), _ptr(slopes), _ptr(gate),
           _i(gate.stride(0) if gate is not None else 0), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs), _i(ctx.max_new),
-          _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _i(int(tiled)), _stream())
+          _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _i(int(tiled)), _ptr(sinks),
+          _i(int(gate_heads)), _f(out_scale), _stream())
 
 
 # ---- routed feed-forward (csrc/routed_ffn.cu) -----------------------------------------------------------------------
 def route(h, router, correction, shared_gate, n_tokens: int, top: int, n_groups: int, keep_groups: int, chosen, weights,
-          shared_scale) -> None:
-    """Per token: softmax over the router's logits, choice among the best groups, `top` experts and their
-    normalised weights; with `shared_gate` [width] also sigmoid(shared_gate . h) into `shared_scale`."""
+          shared_scale, scoring: str = "softmax", group_top: int = 1, renormalize: bool = True) -> None:
+    """Per token: scores over the router's logits (`scoring`: "softmax" over all, or "sigmoid" of each), choice among the
+    best groups (a group's score: the sum of its `group_top` largest), `top` experts and their weights (their scores,
+    divided by their sum if `renormalize`); with `shared_gate` [width] also sigmoid(shared_gate . h) into `shared_scale`."""
+    assert scoring in ("softmax", "sigmoid")
     _need_cuda(h, router, correction, shared_gate, chosen, weights, shared_scale)
     n_routed, width = router.shape
     assert h.stride(1) == 1 and h.shape[1] == width and router.is_contiguous()
@@ -549,12 +560,12 @@ def route(h, router, correction, shared_gate, n_tokens: int, top: int, n_groups:
     assert shared_gate is None or (shared_gate.numel() == width and shared_gate.dtype == router.dtype and shared_gate.is_contiguous())
     _call("core", "mdma_route", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(router), _i(dtype_code(router.dtype)),
           _ptr(correction), _i(dtype_code(correction.dtype) if correction is not None else F32), _ptr(shared_gate),
-          _i(n_tokens), _i(width), _i(n_routed), _i(top), _i(n_groups), _i(keep_groups), _ptr(chosen), _ptr(weights),
-          _ptr(shared_scale), _stream())
+          _i(n_tokens), _i(width), _i(n_routed), _i(top), _i(n_groups), _i(keep_groups), _i(int(scoring == "sigmoid")),
+          _i(group_top), _i(int(renormalize)), _ptr(chosen), _ptr(weights), _ptr(shared_scale), _stream())
 
 
 def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: int, top: int, ff: int, act, x,
-            sorted_scratch=None) -> None:
+            sorted_scratch=None, pair_act: int = ACT_SILU, act_limit: float = 0.0, act_alpha: float = 1.0) -> None:
     """x += sum over each token's chosen experts of weight * expert(h) (identity experts: weight * h).  gate_w, up_w
     [experts * ff, width], down_w [experts * width, ff]; act [tokens * top, ff] scratch in h's dtype.
     `sorted_scratch` = (first [2 * (experts + 1)] ints, order, y): the expert-by-expert kernels (steps of many tokens); else token by token."""
@@ -570,7 +581,7 @@ def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: 
     if sorted_scratch is None:
         _call("core", "mdma_experts_by_token", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(gate_w), _ptr(up_w),
               _ptr(down_w), _i(wd), _ptr(chosen), _ptr(weights), _i(n_tokens), _i(n_experts), _i(top), _i(width), _i(ff),
-              _ptr(act), _ptr(x), _stream(), launches=2)
+              _ptr(act), _ptr(x), _i(pair_act), _f(act_limit), _f(act_alpha), _stream(), launches=2)
         return
     first, order, y = sorted_scratch
     _need_cuda(first, order, y)
@@ -578,7 +589,8 @@ def experts(h, gate_w, up_w, down_w, chosen, weights, n_tokens: int, n_experts: 
     assert y.dtype == torch.float32 and y.is_contiguous() and y.numel() >= n_tokens * top * width
     _call("core", "mdma_experts_sorted", _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(gate_w), _ptr(up_w),
           _ptr(down_w), _i(wd), _ptr(chosen), _ptr(weights), _i(n_tokens), _i(n_experts), _i(top), _i(width), _i(ff),
-          _ptr(first), _ptr(order), _ptr(act), _ptr(y), _ptr(x), _stream(), launches=4)
+          _ptr(first), _ptr(order), _ptr(act), _ptr(y), _ptr(x), _i(pair_act), _f(act_limit), _f(act_alpha), _stream(),
+          launches=4)
 
 
 def experts_gather(h, chosen, n_tokens: int, n_experts: int, top: int, first, order, where, rows) -> None:
@@ -602,3 +614,84 @@ def experts_combine(y, h, chosen, weights, where, n_tokens: int, n_experts: int,
     assert y.dtype == torch.float32 and y.is_contiguous() and x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == width
     _call("core", "mdma_experts_combine", _ptr(y), _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(chosen),
           _ptr(weights), _ptr(where), _i(n_tokens), _i(n_experts), _i(top), _i(width), _ptr(x), _stream())
+
+
+# ---- attention made ready in one pass, per-head gates, a norm on a sublayer's result (csrc/attention_prepare.cu) -------
+def qk_prepare(proj, k_col: int, v_col: int, tok_seq, tok_pos, seq_slot, inv_freq, k_cache, v_cache, page_table,
+               max_pages: int, page_size: int, n_tokens: int, n_heads: int, n_kv_heads: int, dim: int, v_dim: int,
+               rotary_dim: int, interleaved: bool, unit_norm: bool, eps: float, write_kv: bool) -> None:
+    """Rows [q heads | ... k heads at k_col | ... v heads at v_col]: q and k heads are rotated by the token's position
+    (the first `rotary_dim` numbers of each head) and, with `unit_norm`, divided by their root mean square (eps inside
+    the root); q in place, k and v to the token's cache row (`write_kv`)."""
+    _need_cuda(proj, tok_seq, tok_pos, seq_slot, inv_freq, k_cache, v_cache, page_table)
+    assert proj.stride(1) == 1 and (inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2))
+    if write_kv:
+        assert k_cache.dtype == proj.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[-1] == dim and v_cache.shape[-1] == v_dim
+        assert proj.shape[1] >= v_col + n_kv_heads * v_dim and v_col >= k_col + n_kv_heads * dim >= 0
+    _call("core", "mdma_qk_prepare", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(k_col), _i(v_col),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+          _i(max_pages), _i(page_size), _i(n_tokens), _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(rotary_dim),
+          _i(int(interleaved)), _i(int(unit_norm)), _f(eps), _i(int(write_kv)), _stream())
+
+
+def head_gate(out: torch.Tensor, gate: Optional[torch.Tensor], n_rows: int, n_heads: int, v_dim: int, scale: float = 1.0) -> None:
+    """out[t, h * v_dim + d] *= sigmoid(gate[t, h]) * scale in place; gate may be a view of wider rows."""
+    _need_cuda(out, gate)
+    assert out.is_contiguous() and out.shape[1] == n_heads * v_dim
+    assert gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
+    _call("core", "mdma_head_gate", _ptr(out), _ptr(gate), _i(dtype_code(out.dtype)), _i(gate.stride(0) if gate is not None else 0), _i(n_rows),
+          _i(n_heads), _i(v_dim), _f(scale), _stream())
+
+
+def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, n_rows: int,
+                partial: Optional[torch.Tensor] = None, splits: int = 0, split_stride: int = 0) -> None:
+    """x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w; x and y float rows.  With `partial` [splits, rows, width], y is first
+    completed by those sums (a K-split product not yet added up)."""
+    _need_cuda(x, y, w, partial)
+    width = x.shape[1]
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape[1] == width
+    assert w.numel() == width and w.is_contiguous()
+    _call("core", "mdma_rmsnorm_add", _ptr(x), _ptr(y), _ptr(partial), _i(splits if partial is not None else 0),
+          ctypes.c_long(split_stride), _ptr(w), _i(dtype_code(w.dtype)), _i(n_rows), _i(width), _f(eps), _stream())
+
+
+def add_scaled(y: torch.Tensor, z: torch.Tensor, a: float, n_rows: int) -> None:
+    """y[:n_rows] += a * z[:n_rows]; float rows of one width."""
+    _need_cuda(y, z)
+    assert y.dtype == z.dtype == torch.float32 and y.is_contiguous() and z.is_contiguous() and y.shape[1] == z.shape[1]
+    _call("core", "mdma_add_scaled", _ptr(y), _ptr(z), _f(a), ctypes.c_long(n_rows * y.shape[1]), _stream())
+
+
+# ---- linear attention with a decay per head (csrc/linear_attention.cu) -----------------------------------------------------
+def linear_attention_fits(dim: int, vdim: int) -> bool:
+    lib = _build._loaded.get("core") or _build.load("core")
+    cols = lib.mdma_linear_attention_cols(_i(dim), _i(vdim))
+    return 4 * (dim * cols + 2 * 32 * (dim + 1) + 32 * cols + 32 * 33 + 33) <= 200 * 1024
+
+
+def linear_attention(proj, q_col: int, k_col: int, v_col: int, decay, seq_start, seq_slot, state, out, n_seqs: int,
+                     heads: int, dim: int, vdim: int, runs: bool = False) -> None:
+    """S = decay_h S + k v^T, o = S^T q per head over each sequence's rows, q, k, v = SiLU of the columns q_col.., k_col..,
+    v_col.. of `proj`; state [slots, heads * dim * vdim] floats is read and brought up to date; out [T, heads * vdim]
+    floats.  `runs`: the walk a chunk of rows at a time (equal up to rounding)."""
+    _need_cuda(proj, decay, seq_start, seq_slot, state, out)
+    assert proj.stride(1) == 1 and decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * vdim
+    assert proj.shape[1] >= max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim)
+    sp, ss = _state(state)
+    assert state.shape[1] >= heads * dim * vdim
+    _call("core", "mdma_linear_attention", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(q_col), _i(k_col),
+          _i(v_col), _ptr(decay), _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out), _i(n_seqs), _i(heads), _i(dim),
+          _i(vdim), _i(int(runs)), _stream())
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_rows: int, eps: float,
+                  scale: float = 1.0) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) * scale; o float rows, gate may be a view of wider rows."""
+    _need_cuda(o, gate, w, out)
+    width = o.shape[1]
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and out.shape[1] == width
+    assert gate.stride(1) == 1 and gate.shape[1] >= width and w.numel() == width and w.is_contiguous()
+    _call("core", "mdma_gated_rmsnorm", _ptr(o), _ptr(gate), _i(dtype_code(gate.dtype)), _i(gate.stride(0)), _ptr(w),
+          _i(dtype_code(w.dtype)), _ptr(out), _i(dtype_code(out.dtype)), _i(n_rows), _i(width), _f(eps), _f(scale), _stream())

@@ -175,7 +175,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
          w2: Optional[torch.Tensor] = None, m: Optional[int] = None,
          bn: Optional[int] = None, splits: Optional[int] = None, defer: bool = False,
          st: Optional[TensorState] = None, bias: Optional[torch.Tensor] = None,
-         bias2: Optional[torch.Tensor] = None, act: int = ops.ACT_SILU, store_act: bool = False) -> None:
+         bias2: Optional[torch.Tensor] = None, act: int = ops.ACT_SILU, store_act: bool = False,
+         act_limit: float = 0.0, act_alpha: float = 1.0) -> None:
     """out[:m] (=, +=) a[:m] @ w.T (+ bias) on the tensor cores; the gated mode takes gate=w, up=w2 and
     gives act(gate) * up.
     `defer`: if the product is split over K, leave its partial sums for the next kernel
@@ -205,7 +206,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
           _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status),
           _i(int(defer)), ctypes.byref(used), _ptr(st.sk_flags) if EVEN_SPLIT else None,
-          *ops.ending_args(N, bias, bias2, act), _stream(),
+          *ops.ending_args(N, bias, bias2, act, act_limit, act_alpha), _stream(),
           launches=2 if (splits > 1 and not defer) else 1)
     if defer and used.value > 1:
         st.pending = Pending(out, mode, used.value, M, N)
@@ -213,7 +214,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
 
 def gemm_runs(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first: list, n_features: int,
               mode: int = ops.GEMM_STORE, w2: Optional[torch.Tensor] = None, st: Optional[TensorState] = None,
-              act: int = ops.ACT_SILU) -> None:
+              act: int = ops.ACT_SILU, act_limit: float = 0.0, act_alpha: float = 1.0) -> None:
     """Run r = 0.. of rows: out[first[r]:first[r+1]] = a[first[r]:first[r+1]] @ w[r * n_features:(r+1) * n_features].T
     (gated mode: act(gate) * up with w2 stacked likewise).  `first`: a host list of len(runs) + 1 row numbers.  One
     call for all runs: the loop over the products is in the library."""
@@ -235,7 +236,7 @@ def gemm_runs(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first: list, 
     _call("tensor", "mdma_gemm_tc_runs", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), ctypes.c_long(n_features * K),
           _ptr(out), _i(int(out.dtype == torch.float32)), _i(out.stride(0)), arr, _i(n_runs), _i(n_features), _i(K),
           _i(st.sms), _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status),
-          _ptr(st.sk_flags) if EVEN_SPLIT else None, _i(act), _stream(), launches=live)
+          _ptr(st.sk_flags) if EVEN_SPLIT else None, _i(act), _f(act_limit), _f(act_alpha), _stream(), launches=live)
 
 
 def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:

@@ -2,7 +2,9 @@
 feed_forward(norm(x)), the residual stream x kept in float
 (src/model/arch/llama.rs:181-231).  "shift_gated": the same with a token shift
 in front of the mixer and a learned gate on each sublayer's result.  "parallel":
-one norm whose output both sublayers read, x += mixer(h) + feed_forward(h)."""
+one norm whose output both sublayers read, x += mixer(h) + feed_forward(h).
+"sandwich": a norm in front of each sublayer and one on its result,
+x += norm_b(mixer(norm_a(x))); x += norm_d(feed_forward(norm_c(x)))."""
 from __future__ import annotations
 
 import dataclasses
@@ -161,3 +163,51 @@ class ParallelBlock:
         self.mixer.forward(ctx, h, x, view, owns_cache)
         if self.ffn is not None:
             self.ffn.forward(ctx, h, x)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock:
+    """A norm before and after each sublayer:
+
+        x += post1(mixer(norm1(x)));   x += post2(feed_forward(norm2(x)))       (if the layer has one)
+
+    The two norms on the results come from `LayerSpec.extras`: "mixer_post_norm" and "ffn_post_norm"; they must offer
+    `add_normed(ctx, y, x)` (x += norm(y) over float rows).  A sublayer adds its result into a zeroed float buffer
+    through its ordinary `forward`, so any mixer and feed-forward of the registries fits."""
+
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.width = int(spec.mixer_norm.params["width"])
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer)
+        self.mixer_post = NORMS.get(spec.extras["mixer_post_norm"].kind)(spec.extras["mixer_post_norm"])
+        self.ffn_norm = self.ffn = self.ffn_post = None
+        if spec.ffn is not None:
+            self.ffn_norm = NORMS.get(spec.ffn_norm.kind)(spec.ffn_norm)
+            self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn)
+            self.ffn_post = NORMS.get(spec.extras["ffn_post_norm"].kind)(spec.extras["ffn_post_norm"])
+        for norm in (self.mixer_post, self.ffn_post):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError(f"norm {norm.spec.kind!r} cannot follow a sublayer: it has no `add_normed`")
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn, self.ffn_post)
+                if p is not None]
+
+    def workspace(self):
+        return {"normed": (self.width, "act"), "sublayer": (self.width, "f32")}
+
+    def forward(self, ctx, x, view, owns_cache=True):
+        n = ctx.n_tokens
+        h = ctx.buf("normed", self.width)
+        y = ctx.buf("sublayer", self.width, torch.float32)
+        self.mixer_norm.forward(ctx, x, h)
+        y[:n].zero_()
+        self.mixer.forward(ctx, h, y, view, owns_cache)
+        self.mixer_post.add_normed(ctx, y, x)
+        if self.ffn is None:
+            return
+        self.ffn_norm.forward(ctx, x, h)
+        y[:n].zero_()
+        self.ffn.forward(ctx, h, y)
+        self.ffn_post.add_normed(ctx, y, x)

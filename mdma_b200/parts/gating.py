@@ -125,12 +125,13 @@ class LoopInput(Part):
 @JUNCTIONS.register("loop_add")
 class LoopAdd(Part):
     """Before pass t of a looped stack: x <- (x + x0) + step[t] for t > 0, x <- x + step[0] for the first pass.
-    `step` is [passes, width]."""
-    needs_embedding = True
+    `step` is [passes, width].  `add_input` off: only the pass's vector is added, x <- x + step[t], and the
+    embedding's output is not kept."""
 
     def __init__(self, spec):
         super().__init__(spec)
         self.width, self.passes = int(self.params["width"]), int(self.params["passes"])
+        self.needs_embedding = bool(self.params.get("add_input", True))
 
     def tensor_specs(self):
         return {"step": TensorSpec((self.passes, self.width), "vector", "normal")}
@@ -140,7 +141,7 @@ class LoopAdd(Part):
         self.step = tensors["step"]
 
     def forward(self, ctx, x, x0, t: int):
-        ops.loop_add(x, x0 if t > 0 else None, self.step[t], ctx.n_tokens)
+        ops.loop_add(x, x0 if (t > 0 and self.needs_embedding) else None, self.step[t], ctx.n_tokens)
 
     def resident_tensors(self):
         return [self.step]

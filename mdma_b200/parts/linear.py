@@ -15,8 +15,10 @@ from .base import Runtime
 class Linear:
     def __init__(self, weight: torch.Tensor, rt: Runtime, weight2: Optional[torch.Tensor] = None,
                  bias: Optional[torch.Tensor] = None, bias2: Optional[torch.Tensor] = None,
-                 activation: str = "silu"):
+                 activation: str = "silu", act_limit: float = 0.0, act_alpha: float = 1.0):
+        """`act_limit`, `act_alpha`: the constants of the "swish_limit" gated form."""
         self.w, self.w2, self.rt = weight, weight2, rt
+        self.act_limit, self.act_alpha = float(act_limit), float(act_alpha)
         self.bias, self.bias2 = bias, bias2
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not implemented (have {sorted(ops.ACTIVATIONS)})")
@@ -32,12 +34,13 @@ class Linear:
         if self._tensor_ok:
             from .. import ops_tensor
             ops_tensor.gemm(a, self.w, out, mode, self.w2, m, defer=defer, st=self.rt.tc,
-                            bias=self.bias, bias2=self.bias2, act=self.act, store_act=store_act)
+                            bias=self.bias, bias2=self.bias2, act=self.act, store_act=store_act,
+                            act_limit=self.act_limit, act_alpha=self.act_alpha)
         else:
             if self.rt.gemm == "tensor":
                 from .. import ops_tensor
                 ops_tensor.flush_pending(a.device, self.rt.tc)
-            ops.gemm_simt(a, self.w, out, mode, self.w2, m, self.bias, self.bias2, self.act)
+            ops.gemm_simt(a, self.w, out, mode, self.w2, m, self.bias, self.bias2, self.act, self.act_limit, self.act_alpha)
 
     def store(self, a, out, m, defer: bool = False):
         """out = a W^T.  `defer`: a K-split product may leave its partial sums for the

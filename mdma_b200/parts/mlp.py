@@ -7,7 +7,8 @@ activation run as one kernel.  Parameters beyond the reference's Llama:
 `activation` ("silu", "gelu_tanh") and `bias` (a vector added after each of
 the three products).
 
-Dense (`dense_mlp`): x += act(h Wu^T) Wd^T, no gate; `activation` as above."""
+Dense (`dense_mlp`): x += act(h Wu^T) Wd^T, no gate; `activation` as above or "gelu" (the exact one, through erf);
+`bias`: a vector after each of the two products (`up.b`, `down.b`)."""
 from __future__ import annotations
 
 from .. import ops
@@ -69,11 +70,16 @@ class DenseMLP(Part):
         self.hidden = int(self.params["hidden_size"])
         self.inner = int(self.params["intermediate_size"])
         self.activation = str(self.params.get("activation", "gelu_tanh"))
-        if self.activation not in ops.ACTIVATIONS:
-            raise ValueError(f"activation {self.activation!r} is not implemented (have {sorted(ops.ACTIVATIONS)})")
+        if self.activation not in ops.ACTIVATIONS or self.activation == "swish_limit":
+            raise ValueError(f"activation {self.activation!r} is not implemented for a feed-forward without a gate")
+        self.bias = bool(self.params.get("bias", False))
 
     def tensor_specs(self):
-        return {"up": TensorSpec((self.inner, self.hidden)), "down": TensorSpec((self.hidden, self.inner))}
+        specs = {"up": TensorSpec((self.inner, self.hidden)), "down": TensorSpec((self.hidden, self.inner))}
+        if self.bias:
+            specs["up.b"] = TensorSpec((self.inner,), "vector", "normal")
+            specs["down.b"] = TensorSpec((self.hidden,), "vector", "normal")
+        return specs
 
     def workspace(self):
         # a buffer per size: rows of a shared, wider buffer would not be contiguous
@@ -81,8 +87,8 @@ class DenseMLP(Part):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.up = Linear(tensors["up"], rt, activation=self.activation)
-        self.down = Linear(tensors["down"], rt)
+        self.up = Linear(tensors["up"], rt, bias=tensors.get("up.b"), activation=self.activation)
+        self.down = Linear(tensors["down"], rt, bias=tensors.get("down.b"))
 
     def produce(self, ctx, h, out, defer=False):
         """`defer`: the second product may leave K-split partial sums of `out` for the caller's next kernel."""
@@ -96,4 +102,4 @@ class DenseMLP(Part):
         self.down.accumulate(act, x, ctx.n_tokens)
 
     def resident_tensors(self):
-        return [self.up.w, self.down.w]
+        return [t for t in (self.up.w, self.down.w, self.up.bias, self.down.bias) if t is not None]

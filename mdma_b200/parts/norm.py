@@ -1,7 +1,8 @@
 """Norms.  Both read the float residual stream and write the compute dtype.
 
 RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w (src/backend/cpu.rs:388-401;
-no +1 on the weight, no mean subtraction); sums in float.
+no +1 on the weight, no mean subtraction); sums in float.  `add_normed` is the
+same norm on a sublayer's result, added into the residual stream: x += norm(y).
 
 Dynamic tanh: y = tanh(alpha * x) * w + b with a learned scalar alpha; no mean,
 no variance, nothing summed over the row.
@@ -43,6 +44,19 @@ class RMSNorm(Part):
                 return
             ops_tensor.flush_pending(x.device, self.rt.tc)
         ops.rmsnorm(x, self.weight, self.eps, out, rows, n)
+
+    def add_normed(self, ctx, y, x):
+        """x += norm(y), both float rows: the norm on a sublayer's result.  Partial sums that a K-split product left
+        of y are added up on the way."""
+        partial, splits, stride = None, 0, 0
+        if self.rt.gemm == "tensor":
+            from .. import ops_tensor
+            pend = ops_tensor.take_pending(y, ops.GEMM_ACCUMULATE, ctx.n_tokens, self.rt.tc)
+            if pend is not None:
+                partial, splits, stride = pend
+            else:
+                ops_tensor.flush_pending(y.device, self.rt.tc)
+        ops.rmsnorm_add(x, y, self.weight, self.eps, ctx.n_tokens, partial, splits, stride)
 
     def resident_tensors(self):
         return [self.weight]

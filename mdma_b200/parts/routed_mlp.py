@@ -1,10 +1,14 @@
 """A feed-forward of many small gated feed-forwards of which each token uses a few (`routed_mlp`).
 
-Router, in float:  z = R h over all routed outputs, s = softmax(z), choice scores c = s + correction.
-The routed outputs form `groups` equal groups of neighbours; a group's score is its largest c, and only
+Router, in float:  z = R h over all routed outputs, s = softmax(z) (`scoring` "sigmoid": s = sigmoid(z), each
+on its own), choice scores c = s + correction (`correction` off: c = s).
+The routed outputs form `groups` equal groups of neighbours; a group's score is the sum of its `group_top`
+largest c (1, the default: its largest), and only
 members of the `keep_groups` best groups can be chosen (the others count as minus infinity).  The
 `top` eligible outputs with the largest c are chosen; their weights are their s divided by the sum of
-the chosen s (+ 1e-20).  The first `experts` routed outputs are experts, D_e (silu(G_e h) * (U_e h));
+the chosen s (+ 1e-20), or with `renormalize` off their s as they are.  The first `experts` routed outputs are experts,
+D_e (silu(G_e h) * (U_e h)), or with `activation` "swish_limit" D_e (g sigmoid(act_alpha g) (u + 1)) where
+g = min(G_e h, act_limit) and u = U_e h kept within +-act_limit;
 the last `identity` ones have no matrices and return h itself.  The result is the weighted sum.  A
 shared expert of the same form (`shared_ff` > 0) runs for every token and is added, multiplied by
 sigmoid(g . h), one number per token (`shared_gate`).
@@ -49,6 +53,16 @@ class RoutedMLP(Part):
         self.shared_ff = int(p.get("shared_ff", 0) or 0)
         self.shared_gate = bool(p.get("shared_gate", True)) and self.shared_ff > 0
         self.correction = bool(p.get("correction", True))
+        self.scoring = str(p.get("scoring", "softmax"))
+        self.group_top = int(p.get("group_top", 1) or 1)
+        self.renormalize = bool(p.get("renormalize", True))
+        self.activation = str(p.get("activation", "silu"))
+        self.act_limit, self.act_alpha = float(p.get("act_limit", 0.0) or 0.0), float(p.get("act_alpha", 1.0))
+        if self.scoring not in ("softmax", "sigmoid") or not 1 <= self.group_top <= 8:
+            raise ValueError(f"router scoring {self.scoring!r} with groups scored by their {self.group_top} largest is not implemented")
+        if self.activation not in ("silu", "gelu_tanh", "gelu", "swish_limit"):
+            raise ValueError(f"expert activation {self.activation!r} is not implemented")
+        self.pair_act = ops.ACTIVATIONS[self.activation]
         self.n_routed = self.n_experts + self.n_identity
         if not 0 < self.top <= min(self.n_routed, self.MAX_TOP) or self.n_routed > self.MAX_ROUTED:
             raise ValueError(f"top {self.top} of {self.n_routed} routed outputs is outside the router kernel's limits "
@@ -112,7 +126,8 @@ class RoutedMLP(Part):
         self.correction_values = tensors.get("correction")
         self.shared_up = self.shared_down = self.sg = None
         if self.shared_ff:
-            self.shared_up = Linear(tensors["shared.gate"], rt, tensors["shared.up"])
+            self.shared_up = Linear(tensors["shared.gate"], rt, tensors["shared.up"], activation=self.activation,
+                                    act_limit=self.act_limit, act_alpha=self.act_alpha)
             self.shared_down = Linear(tensors["shared.down"], rt)
             if self.shared_gate:
                 self.sg = tensors["shared.sg"].reshape(-1)
@@ -134,7 +149,7 @@ class RoutedMLP(Part):
         act = ctx.buf(names[3], self.top * self.ff)
         scale = ctx.buf(names[6], 1, torch.float32)
         ops.route(h, self.router, self.correction_values, self.sg, n, self.top, self.groups, self.keep_groups, chosen,
-                  weight, scale if self.sg is not None else None)
+                  weight, scale if self.sg is not None else None, self.scoring, self.group_top, self.renormalize)
         if (self.by_products and n >= self.PRODUCTS_FROM and not getattr(ctx, "decode_only", False)
                 and not torch.cuda.is_current_stream_capturing()):
             self._experts_by_products(ctx, h, x, chosen, weight, act, names)
@@ -146,7 +161,7 @@ class RoutedMLP(Part):
             order = ctx.buf(names[2], self.top, torch.float32).view(torch.int32)
             scratch = (self.first, order, ctx.buf(names[4], self.top * self.hidden, torch.float32))
         ops.experts(h, self.w_gate, self.w_up, self.w_down, chosen, weight, n, self.n_experts, self.top, self.ff,
-                    act.view(-1, self.ff), x, scratch)
+                    act.view(-1, self.ff), x, scratch, self.pair_act, self.act_limit, self.act_alpha)
         self._shared(ctx, h, x, scale)
 
     def _experts_by_products(self, ctx, h, x, chosen, weight, act, names):
@@ -159,7 +174,8 @@ class RoutedMLP(Part):
         ops.experts_gather(h, chosen, n, self.n_experts, self.top, self.first, order, where, rows)
         first = self.first[:self.n_experts + 1].tolist()     # how many rows each expert got: read on the host
         from .. import ops_tensor
-        ops_tensor.gemm_runs(rows, self.w_gate, act, first, self.ff, ops.GEMM_SWIGLU, self.w_up, st=self.rt.tc)
+        ops_tensor.gemm_runs(rows, self.w_gate, act, first, self.ff, ops.GEMM_SWIGLU, self.w_up, st=self.rt.tc,
+                             act=self.pair_act, act_limit=self.act_limit, act_alpha=self.act_alpha)
         ops_tensor.gemm_runs(act, self.w_down, y, first, self.hidden, ops.GEMM_STORE, st=self.rt.tc)
         ops.experts_combine(y, h, chosen, weight, where, n, self.n_experts, self.top, x)
 
