@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
     python bench.py --shape llama-2-7b | llama-3.2-1b [--batch B] [--prompt-len P] [--prefill-tokens T]
-    python bench.py --compare gevonex|mogevik [--compare-widths 1024,2048,4096] [--compare-layers 4]
+    python bench.py --compare gevonex|mogevik|tubusun [--compare-widths 1024,2048,4096] [--compare-layers 4]
 
 Prints ONE JSON line.  The default run has the layer sizes of the
 Llama-3.1-8B shape with random bfloat16 weights, a batch of 8 sequences
@@ -25,6 +25,11 @@ of its own; the default workload and its line are unchanged.
 windowed attention with a distance penalty, routed feed-forwards) beside a
 Gevonex and a Llama of the same width, depth and vocabulary and the same
 number of matrix elements a token uses.
+
+`--compare tubusun` does the same for the Tubusun architecture (windowed
+attention with a sink and head gates side by side with linear attention,
+norms around every sublayer, dense and routed feed-forwards) beside a Mogevik
+and a Llama of the same width, depth and vocabulary.
 """
 from __future__ import annotations
 
@@ -168,13 +173,35 @@ def mogevik_config(width: int, layers: int, vocab: int) -> dict:
             "layers": [{"type": kinds[i % 3], "mixer": mixers[kinds[i % 3]], "mlp": mlp} for i in range(layers)]}
 
 
+def tubusun_config(width: int, layers: int, vocab: int) -> dict:
+    """A Tubusun of `layers` layers whose sizes follow the width: query heads of 128 in groups of four over a window of
+    1,024 with half of each head rotated, beside linear-attention heads of 128 x 128 whose decays spread from 0.9 to
+    0.999; a dense feed-forward of 4 x width in the odd layers and sixteen bounded experts of width / 2 in four groups
+    of which three are kept, four per token, in the even ones."""
+    heads = max(1, width // 128)
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 0.09,
+            "mask": {"size": 1024}, "rot": {"dims": 64, "base": 10000.0}}
+    right = {"heads": heads, "dim": 128, "vdim": 128,
+             "decay": [1.0 - 0.1 * (0.01 ** (h / max(1, heads - 1))) for h in range(heads)]}
+    mixer = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}
+    moe = {"kind": "moe", "expert": {"ff": width // 2, "limit": 7.0},
+           "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 3}}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Tubusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if i % 2 else moe} for i in range(layers)]}
+
+
 def expert_share(cfg: dict, name: str, draws: int) -> float:
     """The share of an expert's matrix that a step of `draws` tokens reads (decode: distinct experts among the
     draws, chosen evenly) or, with draws = 0, the share of tokens that use it (prefill)."""
     parts = name.split(".")
     if len(parts) < 3 or parts[1] != "mlp" or not parts[2].startswith("e") or not parts[2][1:].isdigit():
         return 1.0
-    router = cfg["layers"][int(parts[0][1:])]["mlp"]["router"]
+    mlp = cfg["layers"][int(parts[0][1:])]["mlp"]
+    if "router" not in mlp:
+        return 1.0
+    router = mlp["router"]
     n = router["experts"] + (router.get("identity") or 0)
     if draws == 0:
         return router["top"] / n
@@ -211,7 +238,7 @@ def compare(args) -> int:
                 n = 1
                 for d in ts.shape:
                     n *= d
-                routed = cfg.get("architecture") == "Mogevik"
+                routed = cfg.get("architecture") in ("Mogevik", "Tubusun")
                 matrix_bytes += 2 * n * (expert_share(cfg, name, batch) if routed else 1.0)
                 prefill_elements += n * (expert_share(cfg, name, 0) if routed else 1.0)
         # what a decode step moves besides the matrices: every live sequence's fixed-size state is read and written,
@@ -270,13 +297,17 @@ def compare(args) -> int:
     rows = []
     for width in [int(w) for w in args.compare_widths.split(",")]:
         row = {"width": width, "layers": args.compare_layers, "vocab": vocab, "batch": args.batch}
-        if args.compare == "mogevik":
+        if args.compare == "tubusun":
+            row["tubusun"] = measure(tubusun_config(width, args.compare_layers, vocab), args.batch)
+        if args.compare in ("mogevik", "tubusun"):
             row["mogevik"] = measure(mogevik_config(width, args.compare_layers, vocab), args.batch)
-        row["gevonex"] = measure(gevonex_config(width, args.compare_layers, vocab), args.batch)
+        if args.compare != "tubusun":
+            row["gevonex"] = measure(gevonex_config(width, args.compare_layers, vocab), args.batch)
         row["llama"] = measure(llama_like(width, args.compare_layers, vocab), args.batch)
         rows.append(row)
-    print(json.dumps({"compare": ("mogevik beside gevonex and llama" if args.compare == "mogevik" else "gevonex beside llama")
-                      + " at equal width, depth and vocabulary", "dtype": args.dtype,
+    beside = {"tubusun": "tubusun beside mogevik and llama", "mogevik": "mogevik beside gevonex and llama",
+              "gevonex": "gevonex beside llama"}[args.compare]
+    print(json.dumps({"compare": beside + " at equal width, depth and vocabulary", "dtype": args.dtype,
                       "prefill_tokens": T, "decode_after_prompts_of": prompt, "peaks": peak_src,
                       "hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops,
                       "timing": "CUDA events; every step reads its matrices (0.15 GB and more at the default widths), more than the 126 MB of L2, so nothing is flushed",
@@ -303,7 +334,7 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the true 32-bit engine (CUDA-core kernels), for the record; the headline is bfloat16")
-    ap.add_argument("--compare", default=None, choices=["gevonex", "mogevik"],
+    ap.add_argument("--compare", default=None, choices=["gevonex", "mogevik", "tubusun"],
                     help="another program: the named architecture beside a Llama of equal size (see the header)")
     ap.add_argument("--compare-widths", default="1024,2048,4096")
     ap.add_argument("--compare-layers", type=int, default=4)
