@@ -9,8 +9,10 @@ S [dim, v_dim] starting at zero, kept in float per sequence (the site's state) a
 The heads side by side are RMS-normed together with the weight `norm`, multiplied by sigmoid(Wg h), by the
 constant `out_scale`, and projected by Wo.  The decays are parameters (one per head).  The activations, the state, the
 sums over it, the norm and the gate are float in both engines; the projections are one product in the compute dtype.
-Single tokens and the 32-bit engine walk row by row in one fixed order; the serving engine walks prompts of
-`RUNS_FROM` rows or more a chunk of rows at a time.
+Single tokens and the 32-bit engine walk row by row in one fixed order; the serving engine walks portions of
+`CHUNKS_FROM` rows or more a chunk of rows at a time, and long ones in runs of `RUN_ROWS` rows side by side (the
+recurrence is linear in S: every run's last state from zero, then the runs' starting states in order, then every
+run from its start), if the scratch holds the runs' states.
 
 Side by side.  Two mixers read the same rows and their results are added, each times a constant:
 `left_scale * left(h) + right_scale * right(h)`.  A child that takes an `out_scale` applies its constant itself;
@@ -35,7 +37,8 @@ from .linear import Linear
 class LinearAttention(Part):
     graph_safe = True
     takes_out_scale = True
-    RUNS_FROM = 64            # rows of a sequence in a step from which the serving engine walks chunk by chunk
+    CHUNKS_FROM = 16          # rows of a sequence in a step from which the serving engine walks chunk by chunk
+    RUN_ROWS = 128            # rows of a run; sequences of two runs and more are walked as runs side by side
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -77,7 +80,11 @@ class LinearAttention(Part):
     def workspace(self):
         tag = f"{self.row_width}_{self.v_width}"
         return {f"lin_proj_{tag}": (self.row_width, "act"), f"lin_sum_{tag}": (self.v_width, "f32"),
-                f"lin_out_{tag}": (self.v_width, "act")}
+                f"lin_out_{tag}": (self.v_width, "act"), f"lin_runs_{tag}_{self.dim}": (self._run_columns(), "f32")}
+
+    def _run_columns(self) -> int:
+        # scratch for the runs side by side: room for two runs' states per RUN_ROWS rows of a step
+        return -(-2 * self.heads * self.dim * self.v_dim // self.RUN_ROWS)
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
@@ -88,9 +95,9 @@ class LinearAttention(Part):
         self.norm = tensors["norm"]
         self.o = Linear(tensors["o"], rt)
         self.decay_dev = rt.derived(torch.tensor(self.decay, dtype=torch.float64).to(torch.float32))
-        self.fits = ops.linear_attention_fits(self.dim, self.v_dim)
-        if not self.fits:
+        if not ops.linear_attention_fits(self.dim, self.v_dim):
             raise ValueError(f"linear attention heads of {self.dim} x {self.v_dim} do not fit the kernels' shared memory")
+        self.chunks_fit = ops.linear_attention_fits(self.dim, self.v_dim, chunked=True)
 
     def forward(self, ctx, h, x, view, owns_cache=True):
         n = ctx.n_tokens
@@ -99,9 +106,18 @@ class LinearAttention(Part):
         sums = ctx.buf(f"lin_sum_{tag}", self.v_width, torch.float32)
         out = ctx.buf(f"lin_out_{tag}", self.v_width)
         self.proj.store(h, proj, n)
-        runs = proj.dtype != torch.float32 and ctx.max_new >= self.RUNS_FROM
+        # portions of prompts in the serving engine: a chunk of rows at a time, long ones as runs side by side if the
+        # scratch holds their states (it does unless one long prompt comes with many short ones); else, and always in
+        # the 32-bit engine, row by row
+        chunked = self.chunks_fit and proj.dtype != torch.float32 and ctx.max_new >= self.CHUNKS_FROM
+        run_rows, max_runs, scratch = 0, 1, None
+        if chunked and ctx.max_new >= 2 * self.RUN_ROWS:
+            runs = ctx.buf(f"lin_runs_{tag}_{self.dim}", self._run_columns(), torch.float32).view(-1)
+            most = -(-ctx.max_new // self.RUN_ROWS)
+            if ctx.n_seqs * most * self.heads * self.dim * self.v_dim <= runs.numel():
+                run_rows, max_runs, scratch = self.RUN_ROWS, most, runs
         ops.linear_attention(proj, 0, self.k_col, self.v_col, self.decay_dev, ctx.seq_start, ctx.seq_slot, view.state, sums,
-                             ctx.n_seqs, self.heads, self.dim, self.v_dim, runs)
+                             ctx.n_seqs, self.heads, self.dim, self.v_dim, chunked, run_rows, max_runs, scratch)
         ops.gated_rmsnorm(sums, proj[:, self.g_col:], self.norm, out, n, self.eps, self.out_scale)
         self.o.accumulate(out, x, n, defer=False)
 

@@ -417,8 +417,8 @@ def _plain_linear_attention(q, k, v, decay, S0):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,V", [(3, 8, 16), (2, 16, 8), (5, 4, 12), (1, 20, 20), (2, 64, 100), (2, 200, 24)])
 def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, H, D, V):
-    """Three sequences in slots out of order, each brought in portions down to one and two rows, row by row and (where
-    a portion is long) a chunk of rows at a time; outputs and the final state equal the whole-sequence walk in float64;
+    """Three sequences in slots out of order, each brought in portions down to one and two rows, row by row, a chunk of rows at a time,
+    and in runs of rows walked side by side (several runs where a portion is long); outputs and the final state equal the whole-sequence walk in float64;
     a decay of exactly one and a fast one; the floats beyond a slot's own part of the state row are not touched; a
     slot that is zeroed and used again starts clean."""
     from mdma_b200 import ops
@@ -429,7 +429,10 @@ def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, 
     width = 2 * H * D + H * V
     seqs = [(0.8 * torch.randn(n, width + 5, generator=g)).to(dtype) for n in lengths]
     floats = H * D * V
-    for runs in (False, True):
+    for mode in ("rows", "chunks", "runs of 32", "runs of 48"):
+        run_rows = int(mode.split()[-1]) if mode.startswith("runs") else 0
+        most = -(-100 // run_rows) if run_rows else 1
+        scratch = torch.full((3 * most * floats,), float("nan"), device="cuda") if run_rows else None
         state = torch.full((6, floats + 3), float("nan"), device="cuda")
         state[:, :floats] = 0
         got = [[] for _ in seqs]
@@ -441,7 +444,7 @@ def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, 
             proj = _dev(torch.cat([seqs[s][at[s]:at[s] + n] for s, n in zip(live, ns)]), dtype)
             out = torch.full((sum(ns), H * V), float("nan"), device="cuda")
             ops.linear_attention(proj, 0, H * D, 2 * H * D, _dev(decay), st.seq_start, st.seq_slot, state[:, :floats], out,
-                                 len(live), H, D, V, runs and dtype != torch.float32)
+                                 len(live), H, D, V, mode != "rows", run_rows, most, scratch)
             o = 0
             for s, n in zip(live, ns):
                 got[s].append(out[o:o + n].double().cpu())
@@ -453,8 +456,8 @@ def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, 
             v = pt.silu(x[:, 2 * H * D:width]).view(n, H, V)
             want, S = _plain_linear_attention(q, k, v, decay, torch.zeros(H, D, V, dtype=torch.float64))
             size = max(1.0, float(want.abs().max()))
-            assert (torch.cat(got[s]).view(n, H, V) - want).abs().max() < 3e-5 * size, (s, runs)
-            assert (state[slots[s], :floats].double().cpu().view(H, D, V) - S).abs().max() < 3e-5 * max(1.0, float(S.abs().max())), (s, runs)
+            assert (torch.cat(got[s]).view(n, H, V) - want).abs().max() < 3e-5 * size, (s, mode)
+            assert (state[slots[s], :floats].double().cpu().view(H, D, V) - S).abs().max() < 3e-5 * max(1.0, float(S.abs().max())), (s, mode)
         assert torch.isnan(state[:, floats:]).all() and not state[[1, 3, 5], :floats].any()
     # a state that is not zero goes on from where it was; the same rows from a zeroed slot start clean
     S0 = torch.randn(H, D, V, generator=g, dtype=torch.float64)
@@ -467,7 +470,7 @@ def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, 
     st = _Step([40, 40], [7, 0], [1, 0])
     out = torch.empty(80, H * V, device="cuda")
     ops.linear_attention(_dev(torch.cat([rows, rows]), dtype), 0, H * D, 2 * H * D, _dev(decay), st.seq_start, st.seq_slot, state, out,
-                         2, H, D, V, dtype != torch.float32)
+                         2, H, D, V, True)
     for n, start in enumerate((S0, torch.zeros_like(S0))):
         want, _ = _plain_linear_attention(q, k, v, decay, start)
         assert (out[40 * n:40 * n + 40].double().cpu().view(40, H, V) - want).abs().max() < 3e-5 * max(1.0, float(want.abs().max()))
