@@ -13,9 +13,9 @@
 // within a chunk  o_i = decay^(i+1) S^T q_i + sum_(j <= i) decay^(i-j) (q_i . k_j) v_j,  and afterwards
 // S <- decay^n S + sum_j decay^(n-1-j) k_j v_j^T.  Equal to the walk row by row up to rounding.  Long sequences are
 // cut into runs of `run_rows` rows that are walked side by side, since the recurrence is linear in S: pass kLinLocal
-// walks every run but the last from S = 0 and leaves the run's last S in scratch; linear_attention_starts_kernel
-// turns those, in order, into every run's starting S (start[r+1] = decay^run_rows start[r] + local[r]); pass
-// kLinFrom walks every run from its start and writes o, the last run also the sequence's state.
+// walks every run but the last from S = 0 and leaves the run's last S in scratch; pass kLinFrom sums up each run's
+// starting S from those in order (start[r+1] = decay^run_rows start[r] + local[r]), walks the run from there and
+// writes o, the last run also the sequence's state.
 //
 // gated_rmsnorm: out = o / sqrt(mean(o^2) + eps) * w * sigmoid(g) * scale over the heads side by side.
 #include "common.cuh"
@@ -78,22 +78,44 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int row_stride, int q_c
 }
 
 // ---------------------------------------------------------------- a chunk of rows at a time
-// Block = (sequence or run, head, part of the columns), 256 threads.  Shared memory, all floats, every row a
-// multiple of four long so that threads read four neighbours at once: S [dimP][colsP]; q, k [kChunk][dimP + 4];
-// v [kChunk][colsP]; A [kChunk][kChunk + 4]; decay^0 .. decay^kChunk.  Rows and columns beyond the data are zero.
+// Block = (sequence or run, head, part of the columns), 256 threads.  Shared memory, floats, every row a multiple
+// of four long so that threads read four neighbours at once: S [dimP][colsP] (dimP a multiple of 8); q, k
+// [kChunk][dimP + 4]; v [kChunk][colsP]; A [kChunk][kChunk + 4]; decay^0 .. decay^kChunk; one factor per row.  Rows
+// and columns beyond the data are zero.
 //   A[i][j] = decay^(i-j) (q_i . k_j), j <= i: a thread owns two rows and two columns.
 //   o_i[c]  = decay^(i+1) sum_d q_i[d] S[d][c] + sum_j A[i][j] v_j[c]: a thread owns two rows of four columns.
-//   S[d][c] = decay^n S[d][c] + sum_j decay^(n-1-j) k_j[d] v_j[c]: a thread owns four by four entries.
+//   S[d][c] = decay^n S[d][c] + sum_j decay^(n-1-j) k_j[d] v_j[c]: a thread owns eight by four entries.
+// Where every row part starts on a 16-byte boundary (`staged`: bfloat16 rows, sizes and offsets multiples of 8) the
+// next chunk's rows are on their way into a raw buffer (cp.async) while this chunk is computed.
+// Passes over runs: kLinLocal leaves in `run_state[run]` the run's last S from zero (v_j carries the whole factor
+// decay^(rows after j in the run), so S is never rescaled), and the block of a sequence's last run leaves a copy of
+// the sequence's state there instead; kLinFrom starts run r from
+// decay^(r run_rows) state + sum_(p < r) decay^((r-1-p) run_rows) local[p], summed in order.
 constexpr int kChunk = 32;
 constexpr int kAPitch = kChunk + 4;
 enum LinPass : int { kLinWhole = 0, kLinLocal = 1, kLinFrom = 2 };
 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ void fma4(float4& acc, float a, const float4& b) {
     acc.x = fmaf(a, b.x, acc.x); acc.y = fmaf(a, b.y, acc.y); acc.z = fmaf(a, b.z, acc.z); acc.w = fmaf(a, b.w, acc.w);
 }
+__device__ __forceinline__ void scale4(float4& v, float a) { v.x *= a; v.y *= a; v.z *= a; v.w *= a; }
 __device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
     return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, acc))));
+}
+__device__ __forceinline__ void copy16_async(void* dst_shared, const void* src_global) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_shared);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(src_global) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// eight bfloat16 -> the SiLU of each, times `f`, as two float4
+__device__ __forceinline__ void silu8(const uint4& raw, float f, float4& lo, float4& hi) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]), d = __bfloat1622float2(p[3]);
+    lo = make_float4(silu_float(a.x) * f, silu_float(a.y) * f, silu_float(b.x) * f, silu_float(b.y) * f);
+    hi = make_float4(silu_float(c.x) * f, silu_float(c.y) * f, silu_float(d.x) * f, silu_float(d.y) * f);
 }
 
 template <typename T, int PASS>
@@ -102,7 +124,7 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
                               const float* __restrict__ decay, const int* __restrict__ seq_start,
                               const int* __restrict__ seq_slot, float* __restrict__ state, size_t state_stride,
                               float* __restrict__ out, int heads, int dim, int vdim, int cols, int run_rows, int max_runs,
-                              float* __restrict__ run_state) {
+                              float* __restrict__ run_state, int staged) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(16) float sm[];
@@ -111,51 +133,122 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
     const int h = blockIdx.y;
     const int c0 = blockIdx.z * cols, cw = min(cols, vdim - c0);
     int t0 = seq_start[s], t1 = seq_start[s + 1];
+    const size_t head_floats = (size_t)dim * vdim;
+    float* st = state + (size_t)seq_slot[s] * state_stride + (size_t)h * head_floats;
+    float* rs = PASS == kLinWhole ? nullptr : run_state + ((size_t)blockIdx.x * heads + h) * head_floats;
     bool last_run = true;
     if (PASS != kLinWhole) {
         const int runs = (t1 - t0 + run_rows - 1) / run_rows;
         last_run = run == runs - 1;
-        if (run >= runs || (PASS == kLinLocal && last_run)) return;        // the whole block leaves together
+        if (run >= runs) return;                                           // the whole block leaves together
+        if (PASS == kLinLocal && last_run) {                               // the second pass reads the state from here
+            for (int e = threadIdx.x; e < dim * cw; e += blockDim.x) {
+                const size_t at = (size_t)(e / cw) * vdim + c0 + e % cw;
+                rs[at] = st[at];
+            }
+            return;
+        }
         t0 += run * run_rows;
         t1 = min(t1, t0 + run_rows);
     }
     if (t1 <= t0) return;
-    const int dimP = (dim + 3) & ~3, colsP = (cols + 3) & ~3, kd = dimP + 4;
-    const int cg = colsP >> 2, dg = dimP >> 2;
+    const int dimP = (dim + 7) & ~7, colsP = (cols + 3) & ~3, kd = dimP + 4;
+    const int cg = colsP >> 2;
     float* S = sm;                                   // [dimP][colsP]
     float* sq = S + (size_t)dimP * colsP;            // [kChunk][kd]
     float* sk = sq + (size_t)kChunk * kd;            // [kChunk][kd]
     float* sv = sk + (size_t)kChunk * kd;            // [kChunk][colsP]
     float* sa = sv + (size_t)kChunk * colsP;         // [kChunk][kAPitch]
-    float* pw = sa + (size_t)kChunk * kAPitch;       // decay^0 .. decay^kChunk
-    const size_t head_floats = (size_t)dim * vdim;
-    float* st = state + (size_t)seq_slot[s] * state_stride + (size_t)h * head_floats;
-    float* rs = PASS == kLinWhole ? nullptr : run_state + ((size_t)blockIdx.x * heads + h) * head_floats;
-    const float* from = PASS == kLinWhole ? st : rs;
-    for (int e = threadIdx.x; e < dimP * colsP; e += blockDim.x) {
-        const int d = e / colsP, c = e % colsP;
-        S[e] = (PASS != kLinLocal && d < dim && c < cw) ? from[(size_t)d * vdim + c0 + c] : 0.f;
-    }
+    float* pw = sa + (size_t)kChunk * kAPitch;       // decay^0 .. decay^kChunk, then room up to kChunk + 4
+    float* rowf = pw + kChunk + 4;                   // [kChunk] the local pass's factor of each row of the chunk
+    __nv_bfloat16* raw = reinterpret_cast<__nv_bfloat16*>(rowf + kChunk);   // staged: q, k [kChunk][dim], v [kChunk][cols]
     const float dk = decay[h];
     if (threadIdx.x <= kChunk) pw[threadIdx.x] = powf(dk, (float)threadIdx.x);
+    if (PASS == kLinFrom) {
+        // the run's start: the sequence's state and the runs before this one, in order
+        const float dr = powf(dk, (float)run_rows);
+        const float* s0 = run_state + (((size_t)s * max_runs + (size_t)((seq_start[s + 1] - seq_start[s] + run_rows - 1) / run_rows - 1)) * heads + h) * head_floats;
+        const float* first = run_state + ((size_t)s * max_runs * heads + h) * head_floats;
+        const size_t pitch = (size_t)heads * head_floats;
+        for (int e = threadIdx.x; e < dimP * colsP; e += blockDim.x) {
+            const int d = e / colsP, c = e % colsP;
+            float acc = 0.f;
+            if (d < dim && c < cw) {
+                const size_t at = (size_t)d * vdim + c0 + c;
+                acc = s0[at];
+#pragma unroll 4
+                for (int p = 0; p < run; ++p) acc = fmaf(dr, acc, first[(size_t)p * pitch + at]);
+            }
+            S[e] = acc;
+        }
+    } else {
+        for (int e = threadIdx.x; e < dimP * colsP; e += blockDim.x) {
+            const int d = e / colsP, c = e % colsP;
+            S[e] = (PASS == kLinWhole && d < dim && c < cw) ? st[(size_t)d * vdim + c0 + c] : 0.f;
+        }
+    }
     const T* qbase = proj + q_col + h * dim;
     const T* kbase = proj + k_col + h * dim;
     const T* vbase = proj + v_col + h * vdim + c0;
+    const int d8 = dim >> 3, c8 = cw >> 3;          // staged: 16-byte pieces of a row's q or k part, of its v part
+    __nv_bfloat16* rq = raw;
+    __nv_bfloat16* rk = raw + (size_t)kChunk * dim;
+    __nv_bfloat16* rv = rk + (size_t)kChunk * dim;
+    auto issue = [&](int r0, int n) {
+        for (int e = threadIdx.x; e < n * d8; e += blockDim.x) {
+            const int i = e / d8, p = (e % d8) << 3;
+            const size_t at = (size_t)(r0 + i) * row_stride + p;
+            if (PASS != kLinLocal) copy16_async(rq + i * dim + p, qbase + at);
+            copy16_async(rk + i * dim + p, kbase + at);
+        }
+        for (int e = threadIdx.x; e < n * c8; e += blockDim.x) {
+            const int i = e / c8, p = (e % c8) << 3;
+            copy16_async(rv + i * cols + p, vbase + (size_t)(r0 + i) * row_stride + p);
+        }
+        copies_commit();
+    };
+    if (staged) issue(t0, min(kChunk, t1 - t0));
     for (int r0 = t0; r0 < t1; r0 += kChunk) {
         const int n = min(kChunk, t1 - r0);
-        __syncthreads();                             // the chunk before is done with q, k, v (and S, pw are written)
-        for (int e = threadIdx.x; e < kChunk * dimP; e += blockDim.x) {
-            const int i = e / dimP, d = e % dimP;
-            const bool have = i < n && d < dim;
-            const size_t at = (size_t)(r0 + i) * row_stride + d;
-            if (PASS != kLinLocal) sq[i * kd + d] = have ? silu_float(to_float(qbase[at])) : 0.f;
-            sk[i * kd + d] = have ? silu_float(to_float(kbase[at])) : 0.f;
+        if (staged) copies_wait();
+        __syncthreads();       // the chunk before is done with q, k, v; this chunk's raw rows have landed for everyone
+        if (PASS == kLinLocal && threadIdx.x < kChunk) rowf[threadIdx.x] = powf(dk, (float)max(0, t1 - 1 - r0 - (int)threadIdx.x));
+        if (PASS == kLinLocal) __syncthreads();
+        if (staged) {
+            for (int e = threadIdx.x; e < kChunk * d8; e += blockDim.x) {
+                const int i = e / d8, p = (e % d8) << 3;
+                float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+                if (PASS != kLinLocal) {
+                    if (i < n) silu8(*reinterpret_cast<const uint4*>(rq + i * dim + p), 1.0f, lo, hi);
+                    st4(sq + i * kd + p, lo); st4(sq + i * kd + p + 4, hi);
+                    lo = make_float4(0.f, 0.f, 0.f, 0.f); hi = lo;
+                }
+                if (i < n) silu8(*reinterpret_cast<const uint4*>(rk + i * dim + p), 1.0f, lo, hi);
+                st4(sk + i * kd + p, lo); st4(sk + i * kd + p + 4, hi);
+            }
+            for (int e = threadIdx.x; e < kChunk * (colsP >> 3); e += blockDim.x) {
+                const int i = e / (colsP >> 3), p = (e % (colsP >> 3)) << 3;
+                float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+                if (i < n && p < cw) silu8(*reinterpret_cast<const uint4*>(rv + i * cols + p), PASS == kLinLocal ? rowf[i] : 1.0f, lo, hi);
+                st4(sv + i * colsP + p, lo); st4(sv + i * colsP + p + 4, hi);
+            }
+            __syncthreads();
+            if (r0 + kChunk < t1) issue(r0 + kChunk, min(kChunk, t1 - r0 - kChunk));
+        } else {
+            for (int e = threadIdx.x; e < kChunk * dimP; e += blockDim.x) {
+                const int i = e / dimP, d = e % dimP;
+                const bool have = i < n && d < dim;
+                const size_t at = (size_t)(r0 + i) * row_stride + d;
+                if (PASS != kLinLocal) sq[i * kd + d] = have ? silu_float(to_float(qbase[at])) : 0.f;
+                sk[i * kd + d] = have ? silu_float(to_float(kbase[at])) : 0.f;
+            }
+            for (int e = threadIdx.x; e < kChunk * colsP; e += blockDim.x) {
+                const int i = e / colsP, c = e % colsP;
+                const float f = PASS == kLinLocal ? rowf[i] : 1.0f;
+                sv[e] = (i < n && c < cw) ? silu_float(to_float(vbase[(size_t)(r0 + i) * row_stride + c])) * f : 0.f;
+            }
+            __syncthreads();
         }
-        for (int e = threadIdx.x; e < kChunk * colsP; e += blockDim.x) {
-            const int i = e / colsP, c = e % colsP;
-            sv[e] = (i < n && c < cw) ? silu_float(to_float(vbase[(size_t)(r0 + i) * row_stride + c])) : 0.f;
-        }
-        __syncthreads();
         if (PASS != kLinLocal) {
             {   // A: rows 2 ti, 2 ti + 1; columns tj, tj + 16
                 const int ti = threadIdx.x >> 4, tj = threadIdx.x & 15;
@@ -164,13 +257,18 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
                 if (j0 <= i1) {
                     const float* q0 = sq + i0 * kd; const float* q1 = sq + i1 * kd;
                     const float* k0 = sk + j0 * kd; const float* k1 = sk + j1 * kd;
-                    const bool second = j1 <= i1;
-                    for (int d = 0; d < dimP; d += 4) {
-                        const float4 x0 = ld4(q0 + d), x1 = ld4(q1 + d), y0 = ld4(k0 + d);
-                        a00 = dot4(x0, y0, a00); a10 = dot4(x1, y0, a10);
-                        if (second) {
-                            const float4 y1 = ld4(k1 + d);
+                    if (j1 <= i1) {
+#pragma unroll 2
+                        for (int d = 0; d < dimP; d += 4) {
+                            const float4 x0 = ld4(q0 + d), x1 = ld4(q1 + d), y0 = ld4(k0 + d), y1 = ld4(k1 + d);
+                            a00 = dot4(x0, y0, a00); a10 = dot4(x1, y0, a10);
                             a01 = dot4(x0, y1, a01); a11 = dot4(x1, y1, a11);
+                        }
+                    } else {
+#pragma unroll 2
+                        for (int d = 0; d < dimP; d += 4) {
+                            const float4 x0 = ld4(q0 + d), x1 = ld4(q1 + d), y0 = ld4(k0 + d);
+                            a00 = dot4(x0, y0, a00); a10 = dot4(x1, y0, a10);
                         }
                     }
                 }
@@ -186,6 +284,7 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
                 if (i0 >= n) continue;
                 const float* q0 = sq + i0 * kd; const float* q1 = sq + i1 * kd;
                 float4 o0 = make_float4(0.f, 0.f, 0.f, 0.f), o1 = o0;
+#pragma unroll 2
                 for (int d = 0; d < dimP; d += 4) {
                     const float4 x0 = ld4(q0 + d), x1 = ld4(q1 + d);
                     const float4 s0 = ld4(S + (size_t)d * colsP + c), s1 = ld4(S + (size_t)(d + 1) * colsP + c);
@@ -193,9 +292,8 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
                     fma4(o0, x0.x, s0); fma4(o0, x0.y, s1); fma4(o0, x0.z, s2); fma4(o0, x0.w, s3);
                     fma4(o1, x1.x, s0); fma4(o1, x1.y, s1); fma4(o1, x1.z, s2); fma4(o1, x1.w, s3);
                 }
-                const float p0 = pw[i0 + 1], p1 = pw[i1 + 1];
-                o0.x *= p0; o0.y *= p0; o0.z *= p0; o0.w *= p0;
-                o1.x *= p1; o1.y *= p1; o1.z *= p1; o1.w *= p1;
+                scale4(o0, pw[i0 + 1]);
+                scale4(o1, pw[i1 + 1]);
                 for (int j = 0; j <= i1; j += 4) {   // A is zero beyond the diagonal, v beyond the chunk's rows
                     const float4 a0 = ld4(sa + i0 * kAPitch + j), a1 = ld4(sa + i1 * kAPitch + j);
                     const float4 v0 = ld4(sv + j * colsP + c), v1 = ld4(sv + (j + 1) * colsP + c);
@@ -213,54 +311,33 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
                     }
                 }
             }
+            if (PASS == kLinFrom && !last_run && r0 + kChunk >= t1) break;     // nobody reads this run's last S
             __syncthreads();                         // every o has read S before it changes
         }
-        // S: four by four entries a thread
-        const float pn = pw[n];
-        for (int tile = threadIdx.x; tile < dg * cg; tile += blockDim.x) {
-            const int c = (tile % cg) << 2, d = (tile / cg) << 2;
+        // S: eight by four entries a thread
+        const float pn = PASS == kLinLocal ? 1.0f : pw[n];
+        for (int tile = threadIdx.x; tile < (dimP >> 3) * cg; tile += blockDim.x) {
+            const int c = (tile % cg) << 2, d = (tile / cg) << 3;
             float* Sd = S + (size_t)d * colsP + c;
-            float4 s0 = ld4(Sd), s1 = ld4(Sd + colsP), s2 = ld4(Sd + 2 * colsP), s3 = ld4(Sd + 3 * colsP);
-            s0.x *= pn; s0.y *= pn; s0.z *= pn; s0.w *= pn;  s1.x *= pn; s1.y *= pn; s1.z *= pn; s1.w *= pn;
-            s2.x *= pn; s2.y *= pn; s2.z *= pn; s2.w *= pn;  s3.x *= pn; s3.y *= pn; s3.z *= pn; s3.w *= pn;
+            float4 acc[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) { acc[r] = ld4(Sd + r * colsP); if (PASS != kLinLocal) scale4(acc[r], pn); }
+#pragma unroll 2
             for (int j = 0; j < n; ++j) {
-                const float w = pw[n - 1 - j];
-                const float4 kk = ld4(sk + j * kd + d), vv = ld4(sv + j * colsP + c);
-                fma4(s0, w * kk.x, vv); fma4(s1, w * kk.y, vv); fma4(s2, w * kk.z, vv); fma4(s3, w * kk.w, vv);
+                const float4 vv = ld4(sv + j * colsP + c);
+                float4 ka = ld4(sk + j * kd + d), kb = ld4(sk + j * kd + d + 4);
+                if (PASS != kLinLocal) { const float w = pw[n - 1 - j]; scale4(ka, w); scale4(kb, w); }
+                fma4(acc[0], ka.x, vv); fma4(acc[1], ka.y, vv); fma4(acc[2], ka.z, vv); fma4(acc[3], ka.w, vv);
+                fma4(acc[4], kb.x, vv); fma4(acc[5], kb.y, vv); fma4(acc[6], kb.z, vv); fma4(acc[7], kb.w, vv);
             }
-            *reinterpret_cast<float4*>(Sd) = s0;
-            *reinterpret_cast<float4*>(Sd + colsP) = s1;
-            *reinterpret_cast<float4*>(Sd + 2 * colsP) = s2;
-            *reinterpret_cast<float4*>(Sd + 3 * colsP) = s3;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) st4(Sd + r * colsP, acc[r]);
         }
     }
     __syncthreads();
     float* to = PASS == kLinLocal ? rs : (last_run ? st : nullptr);
     if (to != nullptr)
         for (int e = threadIdx.x; e < dim * cw; e += blockDim.x) to[(size_t)(e / cw) * vdim + c0 + e % cw] = S[(e / cw) * colsP + e % cw];
-}
-
-// The runs' starting states, in order: start[0] = the sequence's state, start[r+1] = decay^run_rows start[r] + local[r]
-// (every run but the last is full).  `run_state` holds local[r] on entry and start[r] on return.  A thread per element.
-__global__ void __launch_bounds__(256)
-linear_attention_starts_kernel(const float* __restrict__ decay, const int* __restrict__ seq_start,
-                               const int* __restrict__ seq_slot, const float* __restrict__ state, size_t state_stride,
-                               float* __restrict__ run_state, int heads, size_t head_floats, int run_rows, int max_runs) {
-    chain_release();
-    chain_wait();
-    const size_t state_floats = (size_t)heads * head_floats;
-    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int s = blockIdx.y;
-    if (e >= state_floats) return;
-    const int runs = (seq_start[s + 1] - seq_start[s] + run_rows - 1) / run_rows;
-    const float dr = powf(decay[e / head_floats], (float)run_rows);
-    float cur = state[(size_t)seq_slot[s] * state_stride + e];
-    for (int r = 0; r < runs; ++r) {
-        float* at = run_state + ((size_t)s * max_runs + r) * state_floats + e;
-        const float local = r < runs - 1 ? *at : 0.f;
-        *at = cur;
-        cur = fmaf(dr, cur, local);
-    }
 }
 
 template <typename TG, typename TW, typename TO>
@@ -283,9 +360,10 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const TG* __restrict__ gate, i
 
 static size_t scan_smem(int dim, int cols) { return sizeof(float) * ((size_t)dim * cols + 2 * dim + cols + 256); }
 static size_t chunk_smem(int dim, int cols) {
-    const size_t dimP = (dim + 3) & ~3, colsP = (cols + 3) & ~3;
+    const size_t dimP = (dim + 7) & ~7, colsP = (cols + 3) & ~3;
     return sizeof(float) * (dimP * colsP + 2 * (size_t)kChunk * (dimP + 4) + (size_t)kChunk * colsP +
-                            (size_t)kChunk * kAPitch + kChunk + 4);
+                            (size_t)kChunk * kAPitch + kChunk + 4 + kChunk) +
+           sizeof(__nv_bfloat16) * (size_t)kChunk * (2 * (size_t)dim + cols);       // the raw rows on their way
 }
 constexpr size_t kLinSmemMost = 200 * 1024;
 
@@ -342,21 +420,19 @@ int mdma_linear_attention(const void* proj, int dtype, int row_stride, int q_col
     } else {
         run_rows = 0; max_runs = 1;
     }
+    const int staged = dtype == ::mdma::kBF16 && dim % 8 == 0 && vdim % 8 == 0 && cols % 8 == 0 && q_col % 8 == 0 &&
+                       k_col % 8 == 0 && v_col % 8 == 0 && row_stride % 8 == 0 && ((uintptr_t)proj & 15) == 0;
 #define MDMA_LA_CHUNK(PASS_, what)                                                                                        \
     MDMA_DISPATCH_DTYPE(dtype, T, {                                                                                       \
         static bool raised = false;                                                                                       \
         if (!raised) { cudaFuncSetAttribute(linear_attention_chunk_kernel<T, PASS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLinSmemMost); raised = true; } \
         launch_chained(linear_attention_chunk_kernel<T, PASS_>, grid, dim3(256), smem, stream, (const T*)proj, row_stride, \
                        q_col, k_col, v_col, decay, seq_start, seq_slot, state, (size_t)state_stride, out, heads, dim, vdim, \
-                       cols, run_rows, max_runs, scratch);                                                                \
+                       cols, run_rows, max_runs, scratch, staged);                                                        \
     });                                                                                                                   \
     MDMA_LAUNCH_OK(what)
     if (run_rows > 0) {
         MDMA_LA_CHUNK(kLinLocal, "linear_attention (runs from zero)");
-        launch_chained(linear_attention_starts_kernel, dim3((unsigned)((heads * head_floats + 255) / 256), n_seqs), dim3(256), 0,
-                       stream, decay, seq_start, seq_slot, (const float*)state, (size_t)state_stride, scratch, heads, head_floats,
-                       run_rows, max_runs);
-        MDMA_LAUNCH_OK("linear_attention_starts");
         MDMA_LA_CHUNK(kLinFrom, "linear_attention (runs from their starts)");
         return 0;
     }

@@ -689,7 +689,7 @@ def linear_attention(proj, q_col: int, k_col: int, v_col: int, decay, seq_start,
     _call("core", "mdma_linear_attention", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(q_col), _i(k_col),
           _i(v_col), _ptr(decay), _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out), _i(n_seqs), _i(heads), _i(dim),
           _i(vdim), _i(int(chunked)), _i(run_rows), _i(max_runs), _ptr(scratch),
-          ctypes.c_long(scratch.numel() if scratch is not None else 0), _stream(), launches=3 if run_rows > 0 else 1)
+          ctypes.c_long(scratch.numel() if scratch is not None else 0), _stream(), launches=2 if run_rows > 0 else 1)
 
 
 def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_rows: int, eps: float,
