@@ -103,8 +103,10 @@ class Attention(Part):
     def check_limits(self, rt):
         """Sizes no kernel of this library takes are refused when the engine is built, before
         anything is loaded (src/model/arch/llama/preflight.rs:35-42)."""
-        if max(self.head_dim, self.v_dim) > self.MAX_HEAD_DIM:
-            raise ValueError(f"head sizes {self.head_dim} / {self.v_dim} are beyond the attention kernels' limit of {self.MAX_HEAD_DIM}")
+        if self.head_dim > self.MAX_HEAD_DIM:
+            raise ValueError(f"head_dim {self.head_dim} is beyond the attention kernels' limit of {self.MAX_HEAD_DIM}")
+        if self.v_dim > self.MAX_HEAD_DIM:
+            raise ValueError(f"v_dim {self.v_dim} is beyond the attention kernels' limit of {self.MAX_HEAD_DIM}")
 
     def fused_tensors(self):
         # one product for q, k and v (and the heads' gate numbers)
