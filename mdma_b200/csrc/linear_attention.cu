@@ -77,6 +77,67 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int row_stride, int q_c
     for (int e = threadIdx.x; e < dim * cw; e += blockDim.x) st[(size_t)(e / cw) * vdim + c0 + e % cw] = S[(e / cw) * cols + e % cw];
 }
 
+// ---------------------------------------------------------------- single rows
+// Steps that bring one row a sequence: S never enters shared memory.  Block = (sequence, head, kStepCols columns), 256
+// threads; a thread owns four neighbouring columns of every 64th row of S, reads them from the state row, brings them up
+// to date, writes them back and sums its part of o; the 64 parts of a column are added in one fixed order.  A sequence
+// of several rows is walked row by row from the state row itself (right, but slow: the serving engine takes this kernel
+// only where no sequence brings more than one row).
+constexpr int kStepCols = 16, kStepQuads = kStepCols / 4, kStepGroups = 256 / kStepQuads;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_attention_step_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_col, int v_col,
+                             const float* __restrict__ decay, const int* __restrict__ seq_start,
+                             const int* __restrict__ seq_slot, float* __restrict__ state, size_t state_stride,
+                             float* __restrict__ out, int heads, int dim, int vdim) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float sm[];
+    const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kStepCols;
+    const int t0 = seq_start[s], t1 = seq_start[s + 1];
+    if (t1 <= t0) return;
+    float* sq = sm;                    // [dim]
+    float* sk = sq + dim;              // [dim]
+    float* sv = sk + dim;              // [kStepCols]
+    float* red = sv + kStepCols;       // [kStepGroups][kStepCols]
+    const int quad = threadIdx.x % kStepQuads, rg = threadIdx.x / kStepQuads;
+    const int c = c0 + 4 * quad;
+    const bool active = c < vdim;      // vdim is a multiple of four
+    float* st = state + (size_t)seq_slot[s] * state_stride + (size_t)h * dim * vdim + c;
+    const float dk = decay[h];
+    for (int t = t0; t < t1; ++t) {
+        const T* row = proj + (size_t)t * row_stride;
+        for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+            sq[e] = silu_float(to_float(row[q_col + h * dim + e]));
+            sk[e] = silu_float(to_float(row[k_col + h * dim + e]));
+        }
+        if (threadIdx.x < kStepCols) sv[threadIdx.x] = c0 + threadIdx.x < vdim ? silu_float(to_float(row[v_col + h * vdim + c0 + threadIdx.x])) : 0.f;
+        __syncthreads();
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (active) {
+            const float4 v4 = *reinterpret_cast<const float4*>(sv + 4 * quad);
+            for (int i = rg; i < dim; i += kStepGroups) {
+                float4 e = *reinterpret_cast<const float4*>(st + (size_t)i * vdim);
+                const float ki = sk[i], qi = sq[i];
+                e.x = fmaf(dk, e.x, ki * v4.x); e.y = fmaf(dk, e.y, ki * v4.y);
+                e.z = fmaf(dk, e.z, ki * v4.z); e.w = fmaf(dk, e.w, ki * v4.w);
+                *reinterpret_cast<float4*>(st + (size_t)i * vdim) = e;
+                acc.x = fmaf(e.x, qi, acc.x); acc.y = fmaf(e.y, qi, acc.y);
+                acc.z = fmaf(e.z, qi, acc.z); acc.w = fmaf(e.w, qi, acc.w);
+            }
+        }
+        *reinterpret_cast<float4*>(red + rg * kStepCols + 4 * quad) = acc;
+        __syncthreads();
+        if (threadIdx.x < kStepCols && c0 + threadIdx.x < vdim) {
+            float o = 0.f;
+            for (int g = 0; g < kStepGroups; ++g) o += red[g * kStepCols + threadIdx.x];
+            out[(size_t)t * heads * vdim + (size_t)h * vdim + c0 + threadIdx.x] = o;
+        }
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------- a chunk of rows at a time
 // Block = (sequence or run, head, part of the columns), 256 threads.  Shared memory, floats, every row a multiple
 // of four long so that threads read four neighbours at once: S [dimP][colsP] (dimP a multiple of 8); q, k
@@ -94,6 +155,7 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int row_stride, int q_c
 constexpr int kChunk = 32;
 constexpr int kAPitch = kChunk + 4;
 enum LinPass : int { kLinWhole = 0, kLinLocal = 1, kLinFrom = 2 };
+constexpr int kLinSingleRows = 2;      // value of the launcher's `chunked` that asks for the single-row kernel
 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
@@ -388,7 +450,8 @@ int mdma_linear_attention_fits(int dim, int vdim, int chunked) {
 
 // proj rows hold q at q_col + head * dim, k at k_col + head * dim, v at v_col + head * vdim (before their SiLU);
 // state [slots][heads * dim * vdim] floats; out [n_tokens][heads * vdim] floats.  chunked == 0: row by row.
-// chunked != 0: a chunk of rows at a time, and with run_rows > 0 in runs of that many rows side by side
+// chunked == 2 (kLinSingleRows): the kernel for steps of one row a sequence (row by row where the state's layout does
+// not allow its 16-byte accesses).  chunked == 1: a chunk of rows at a time, and with run_rows > 0 in runs of that many rows side by side
 // (`max_runs`: the most runs of a sequence; `scratch`: n_seqs * max_runs * heads * dim * vdim floats).
 int mdma_linear_attention(const void* proj, int dtype, int row_stride, int q_col, int k_col, int v_col, const float* decay,
                           const int* seq_start, const int* seq_slot, float* state, long state_stride, float* out,
@@ -397,6 +460,21 @@ int mdma_linear_attention(const void* proj, int dtype, int row_stride, int q_col
     MDMA_REQUIRE(n_seqs >= 0 && heads > 0 && dim > 0 && vdim > 0, "linear_attention: bad sizes");
     MDMA_REQUIRE(n_seqs <= 65535 * 32 && heads <= 65535, "linear_attention: too many sequences or heads");
     if (n_seqs == 0) return 0;
+    if (chunked == kLinSingleRows) {
+        // four neighbouring floats of a state row at a time: every head's part and every slot's row start on 16 bytes
+        const bool fits = vdim % 4 == 0 && state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0 && dim <= 4096;
+        if (fits) {
+            const size_t step_smem = (size_t)(2 * dim + kStepCols + kStepGroups * kStepCols) * sizeof(float);
+            dim3 step_grid(n_seqs, heads, (vdim + kStepCols - 1) / kStepCols);
+            MDMA_DISPATCH_DTYPE(dtype, T, {
+                launch_chained(linear_attention_step_kernel<T>, step_grid, dim3(256), step_smem, stream, (const T*)proj, row_stride,
+                               q_col, k_col, v_col, decay, seq_start, seq_slot, state, (size_t)state_stride, out, heads, dim, vdim);
+            });
+            MDMA_LAUNCH_OK("linear_attention (single rows)");
+            return 0;
+        }
+        chunked = 0;
+    }
     const int cols = mdma_linear_attention_cols(dim, vdim);
     const size_t smem = chunked ? chunk_smem(dim, cols) : scan_smem(dim, cols);
     MDMA_REQUIRE(smem <= kLinSmemMost, "linear_attention: heads of %d x %d do not fit a block's shared memory", dim, vdim);

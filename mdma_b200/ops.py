@@ -672,23 +672,24 @@ def linear_attention_fits(dim: int, vdim: int, chunked: bool = False) -> bool:
 
 def linear_attention(proj, q_col: int, k_col: int, v_col: int, decay, seq_start, seq_slot, state, out, n_seqs: int,
                      heads: int, dim: int, vdim: int, chunked: bool = False, run_rows: int = 0, max_runs: int = 1,
-                     scratch=None) -> None:
+                     scratch=None, single: bool = False) -> None:
     """S = decay_h S + k v^T, o = S^T q per head over each sequence's rows, q, k, v = SiLU of the columns q_col.., k_col..,
     v_col.. of `proj`; state [slots, heads * dim * vdim] floats is read and brought up to date; out [T, heads * vdim]
     floats.  `chunked`: the walk a chunk of rows at a time, and with `run_rows` > 0 in runs of that many rows side by
-    side (`max_runs`: the most runs of a sequence; `scratch`: n_seqs * max_runs * heads * dim * vdim floats).  Equal
-    up to rounding."""
+    side (`max_runs`: the most runs of a sequence; `scratch`: n_seqs * max_runs * heads * dim * vdim floats); `single`:
+    the kernel for steps in which no sequence brings more than one row.  Equal up to rounding."""
     _need_cuda(proj, decay, seq_start, seq_slot, state, out)
     _need_cuda(scratch)
     assert proj.stride(1) == 1 and decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous()
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * vdim
     assert proj.shape[1] >= max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim)
     assert run_rows == 0 or (chunked and scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous())
+    assert not (single and chunked)
     sp, ss = _state(state)
     assert state.shape[1] >= heads * dim * vdim
     _call("core", "mdma_linear_attention", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(q_col), _i(k_col),
           _i(v_col), _ptr(decay), _ptr(seq_start), _ptr(seq_slot), sp, ss, _ptr(out), _i(n_seqs), _i(heads), _i(dim),
-          _i(vdim), _i(int(chunked)), _i(run_rows), _i(max_runs), _ptr(scratch),
+          _i(vdim), _i(2 if single else int(chunked)), _i(run_rows), _i(max_runs), _ptr(scratch),
           ctypes.c_long(scratch.numel() if scratch is not None else 0), _stream(), launches=2 if run_rows > 0 else 1)
 
 

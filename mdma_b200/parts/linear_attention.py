@@ -9,7 +9,8 @@ S [dim, v_dim] starting at zero, kept in float per sequence (the site's state) a
 The heads side by side are RMS-normed together with the weight `norm`, multiplied by sigmoid(Wg h), by the
 constant `out_scale`, and projected by Wo.  The decays are parameters (one per head).  The activations, the state, the
 sums over it, the norm and the gate are float in both engines; the projections are one product in the compute dtype.
-Single tokens and the 32-bit engine walk row by row in one fixed order; the serving engine walks portions of
+The 32-bit engine and short portions walk row by row in one fixed order; single tokens in the serving engine update
+the state row in place without staging it; the serving engine walks portions of
 `CHUNKS_FROM` rows or more a chunk of rows at a time, and long ones in runs of `RUN_ROWS` rows side by side (the
 recurrence is linear in S: every run's last state from zero, then the runs' starting states in order, then every
 run from its start), if the scratch holds the runs' states.
@@ -117,7 +118,8 @@ class LinearAttention(Part):
             if ctx.n_seqs * most * self.heads * self.dim * self.v_dim <= runs.numel():
                 run_rows, max_runs, scratch = self.RUN_ROWS, most, runs
         ops.linear_attention(proj, 0, self.k_col, self.v_col, self.decay_dev, ctx.seq_start, ctx.seq_slot, view.state, sums,
-                             ctx.n_seqs, self.heads, self.dim, self.v_dim, chunked, run_rows, max_runs, scratch)
+                             ctx.n_seqs, self.heads, self.dim, self.v_dim, chunked, run_rows, max_runs, scratch,
+                             single=ctx.max_new == 1 and proj.dtype != torch.float32)
         ops.gated_rmsnorm(sums, proj[:, self.g_col:], self.norm, out, n, self.eps, self.out_scale)
         self.o.accumulate(out, x, n, defer=False)
 

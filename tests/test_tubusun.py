@@ -417,7 +417,8 @@ def _plain_linear_attention(q, k, v, decay, S0):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,V", [(3, 8, 16), (2, 16, 8), (5, 4, 12), (1, 20, 20), (2, 64, 100), (2, 200, 24)])
 def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, H, D, V):
-    """Three sequences in slots out of order, each brought in portions down to one and two rows, row by row, a chunk of rows at a time,
+    """Three sequences in slots out of order, each brought in portions down to one and two rows, row by row, by the kernel
+    for single rows, a chunk of rows at a time,
     and in runs of rows walked side by side (several runs where a portion is long); outputs and the final state equal the whole-sequence walk in float64;
     a decay of exactly one and a fast one; the floats beyond a slot's own part of the state row are not touched; a
     slot that is zeroed and used again starts clean."""
@@ -429,11 +430,12 @@ def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, 
     width = 2 * H * D + H * V
     seqs = [(0.8 * torch.randn(n, width + 5, generator=g)).to(dtype) for n in lengths]
     floats = H * D * V
-    for mode in ("rows", "chunks", "runs of 32", "runs of 48"):
+    for mode in ("rows", "singles", "chunks", "runs of 32", "runs of 48"):
         run_rows = int(mode.split()[-1]) if mode.startswith("runs") else 0
         most = -(-100 // run_rows) if run_rows else 1
         scratch = torch.full((3 * most * floats,), float("nan"), device="cuda") if run_rows else None
-        state = torch.full((6, floats + 3), float("nan"), device="cuda")
+        # the single-row kernel reads four floats at a time: its rows start on 16 bytes (else it is the walk row by row)
+        state = torch.full((6, floats + (4 if mode == "singles" else 3)), float("nan"), device="cuda")
         state[:, :floats] = 0
         got = [[] for _ in seqs]
         at = [0, 0, 0]
@@ -444,7 +446,8 @@ def test_linear_attention_in_portions_slots_reused_and_runs_side_by_side(dtype, 
             proj = _dev(torch.cat([seqs[s][at[s]:at[s] + n] for s, n in zip(live, ns)]), dtype)
             out = torch.full((sum(ns), H * V), float("nan"), device="cuda")
             ops.linear_attention(proj, 0, H * D, 2 * H * D, _dev(decay), st.seq_start, st.seq_slot, state[:, :floats], out,
-                                 len(live), H, D, V, mode != "rows", run_rows, most, scratch)
+                                 len(live), H, D, V, mode not in ("rows", "singles"), run_rows, most, scratch,
+                                 single=mode == "singles")
             o = 0
             for s, n in zip(live, ns):
                 got[s].append(out[o:o + n].double().cpu())
