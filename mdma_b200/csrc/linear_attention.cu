@@ -232,16 +232,35 @@ linear_attention_chunk_kernel(const T* __restrict__ proj, int row_stride, int q_
         const float* s0 = run_state + (((size_t)s * max_runs + (size_t)((seq_start[s + 1] - seq_start[s] + run_rows - 1) / run_rows - 1)) * heads + h) * head_floats;
         const float* first = run_state + ((size_t)s * max_runs * heads + h) * head_floats;
         const size_t pitch = (size_t)heads * head_floats;
-        for (int e = threadIdx.x; e < dimP * colsP; e += blockDim.x) {
-            const int d = e / colsP, c = e % colsP;
-            float acc = 0.f;
-            if (d < dim && c < cw) {
-                const size_t at = (size_t)d * vdim + c0 + c;
-                acc = s0[at];
+        if (((vdim | cw | c0) & 3) == 0 && ((uintptr_t)run_state & 15) == 0) {
+            // four neighbouring columns a thread: every earlier run's part is read 16 bytes at a time, four runs in flight
+            for (int e = threadIdx.x; e < dimP * cg; e += blockDim.x) {
+                const int d = e / cg, c = (e % cg) << 2;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (d < dim && c < cw) {
+                    const size_t at = (size_t)d * vdim + c0 + c;
+                    acc = ld4(s0 + at);
 #pragma unroll 4
-                for (int p = 0; p < run; ++p) acc = fmaf(dr, acc, first[(size_t)p * pitch + at]);
+                    for (int p = 0; p < run; ++p) {
+                        const float4 l = ld4(first + (size_t)p * pitch + at);
+                        acc.x = fmaf(dr, acc.x, l.x); acc.y = fmaf(dr, acc.y, l.y);
+                        acc.z = fmaf(dr, acc.z, l.z); acc.w = fmaf(dr, acc.w, l.w);
+                    }
+                }
+                st4(S + (size_t)d * colsP + c, acc);
             }
-            S[e] = acc;
+        } else {
+            for (int e = threadIdx.x; e < dimP * colsP; e += blockDim.x) {
+                const int d = e / colsP, c = e % colsP;
+                float acc = 0.f;
+                if (d < dim && c < cw) {
+                    const size_t at = (size_t)d * vdim + c0 + c;
+                    acc = s0[at];
+#pragma unroll 4
+                    for (int p = 0; p < run; ++p) acc = fmaf(dr, acc, first[(size_t)p * pitch + at]);
+                }
+                S[e] = acc;
+            }
         }
     } else {
         for (int e = threadIdx.x; e < dimP * colsP; e += blockDim.x) {
