@@ -40,9 +40,11 @@ from . import llama_arch  # noqa: E402,F401  registers the Llama architecture
 from . import gevonex_arch  # noqa: E402,F401  registers the Gevonex architecture
 from . import mogevik_arch  # noqa: E402,F401  registers the Mogevik architecture
 from . import tubusun_arch  # noqa: E402,F401  registers the Tubusun architecture
+from . import fizadra_arch  # noqa: E402,F401  registers the Fizadra architecture
+from .fizadra import FizadraConfig  # noqa: E402
 from .gevonex import GevonexConfig  # noqa: E402
 from .mogevik import MogevikConfig  # noqa: E402
 from .tubusun import TubusunConfig  # noqa: E402
 
-__all__ = ["Architecture", "ConfigError", "GevonexConfig", "LlamaConfig", "MogevikConfig", "RopeScaling", "RegistryError", "TubusunConfig",
+__all__ = ["Architecture", "ConfigError", "FizadraConfig", "GevonexConfig", "LlamaConfig", "MogevikConfig", "RopeScaling", "RegistryError", "TubusunConfig",
            "architecture_name", "load_config", "read_config_json"]

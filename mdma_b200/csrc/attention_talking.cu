@@ -1,0 +1,234 @@
+// Attention whose heads talk to one another before the softmax.
+//
+// qk_norm_rotate: a token's fused projection row [q heads | k heads | v heads] is made ready in one pass.  Every q and
+// k head is (if asked) divided by its root mean square, x / sqrt(mean(x^2) + eps), and multiplied by a weight vector
+// shared by all heads, THEN its first `rotary_dim` numbers are turned by the token's position (pairs (2i, 2i+1) or
+// (i, i + rotary_dim/2), cos and sin times `magnitude`).  q is written back in place; k and v go to the token's row
+// of the paged cache (value heads may have a size of their own).
+//
+// talking_attention: raw scores s_g = (q_g . k_kv(g)) * scale of ALL query heads g for a key are mixed by a matrix,
+// s'_h = sum_g T[h, g] s_g, before the softmax of head h; a query at position p sees the keys up to p; the
+// denominator of head h also holds exp(sink_h) when sinks are given (a sink of 0 adds one); the result of head h is
+// sum_j p'_hj v_kv(h),j.  Without T the heads are independent.
+//
+// Plain kernel: a block per token, a warp per head, keys in position order 32 at a time (every warp its head's raw
+// scores into shared memory; then every warp mixes its own row, folds the 32 into its running maximum, sum and
+// weighted value sum).  Everything in float in one fixed order: the result of a token does not depend on the
+// step's cut or on the batch.
+//
+// Tiled kernel: a block takes 16 consecutive rows of one sequence and all heads; keys and values of a kv head are
+// staged 32 keys at a time in shared memory as float, raw scores of all heads for the 16 x 32 tile are kept in shared
+// memory, mixed, and folded row by row.  Steps of many rows in the serving engine.
+#include "common.cuh"
+
+namespace mdma {
+
+constexpr int kTalkMaxDim = 256, kTalkMaxHeads = 32, kPrepWarpsT = 4;
+
+__device__ __forceinline__ float talk_weight(const void* w, int dtype, int e) {
+    if (w == nullptr) return 1.0f;
+    return dtype == kF32 ? reinterpret_cast<const float*>(w)[e] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[e]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarpsT * 32)
+qk_norm_rotate_kernel(T* __restrict__ proj, int row_stride, int k_col, int v_col, const int* __restrict__ tok_seq,
+                      const int* __restrict__ tok_pos, const int* __restrict__ seq_slot, const float* __restrict__ inv_freq,
+                      float magnitude, const void* __restrict__ q_w, const void* __restrict__ k_w, int w_dtype, int norm,
+                      float eps, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ page_table,
+                      int max_pages, int page_size, int n_heads, int n_kv_heads, int dim, int v_dim, int rotary_dim,
+                      int interleaved, int write_kv) {
+    chain_release();
+    chain_wait();
+    __shared__ float sines[kTalkMaxDim / 2], cosines[kTalkMaxDim / 2];
+    __shared__ float rows[kPrepWarpsT][kTalkMaxDim];
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = rotary_dim / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sines[i] = s * magnitude;
+        cosines[i] = c * magnitude;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    const int head = blockIdx.y * kPrepWarpsT + warp;
+    if (head >= total) return;
+    T* row = proj + (size_t)t * row_stride;
+    size_t cache_row = 0;
+    if (write_kv) {
+        const int slot = seq_slot[tok_seq[t]];
+        cache_row = ((size_t)page_table[(size_t)slot * max_pages + pos / page_size] * page_size + (size_t)(pos % page_size)) * n_kv_heads;
+    }
+    if (head >= n_heads + n_kv_heads) {                 // a value head: copied as it is
+        const int g = head - n_heads - n_kv_heads;
+        const T* src = row + v_col + (size_t)g * v_dim;
+        T* dst = v_cache + (cache_row + g) * v_dim;
+        for (int d = lane; d < v_dim; d += 32) dst[d] = src[d];
+        return;
+    }
+    const bool is_q = head < n_heads;
+    T* src = is_q ? row + (size_t)head * dim : row + k_col + (size_t)(head - n_heads) * dim;
+    T* dst = is_q ? src : k_cache + (cache_row + (head - n_heads)) * dim;
+    float* v = rows[warp];
+    float sq = 0.f;
+    for (int d = lane; d < dim; d += 32) {
+        v[d] = to_float(src[d]);
+        sq = fmaf(v[d], v[d], sq);
+    }
+    if (norm) {
+        const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)dim + eps);
+        const void* w = is_q ? q_w : k_w;
+        for (int d = lane; d < dim; d += 32) v[d] = v[d] * inv * talk_weight(w, w_dtype, d);
+    }
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {
+        const int d0 = interleaved ? 2 * i : i, d1 = interleaved ? 2 * i + 1 : i + half;
+        const float a = v[d0], b = v[d1], s = sines[i], c = cosines[i];
+        v[d0] = a * c - b * s;
+        v[d1] = b * c + a * s;
+    }
+    __syncwarp();
+    for (int d = lane; d < dim; d += 32) dst[d] = from_float<T>(v[d]);
+}
+
+// Plain: block = token, warp = head.
+template <typename T>
+__global__ void __launch_bounds__(kTalkMaxHeads * 32)
+talking_attention_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_cache,
+                         const T* __restrict__ v_cache, const float* __restrict__ talk, const float* __restrict__ sinks,
+                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+                         const int* __restrict__ page_table, int max_pages, int page_size, T* __restrict__ out, int n_heads,
+                         int n_kv_heads, int dim, int v_dim, int window, float scale) {
+    chain_release();
+    chain_wait();
+    __shared__ float raw[kTalkMaxHeads][33];
+    const int t = blockIdx.x;
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int pos = tok_pos[t];
+    const int slot = seq_slot[tok_seq[t]];
+    const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+    float qv[kTalkMaxDim / 32], acc[kTalkMaxDim / 32];
+    const T* qp = q + (size_t)t * q_row_stride + (size_t)h * dim;
+#pragma unroll
+    for (int j = 0; j < kTalkMaxDim / 32; ++j) {
+        const int d = lane + 32 * j;
+        qv[j] = d < dim ? to_float(qp[d]) : 0.f;
+        acc[j] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    const int* pages = page_table + (size_t)slot * max_pages;
+    for (int p0 = first; p0 <= pos; p0 += 32) {
+        const int nk = min(32, pos + 1 - p0);
+        float mine = 0.f;
+        for (int k = 0; k < nk; ++k) {
+            const int p = p0 + k;
+            const T* kp = k_cache + (((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh) * dim;
+            float part = 0.f;
+#pragma unroll
+            for (int j = 0; j < kTalkMaxDim / 32; ++j) {
+                const int d = lane + 32 * j;
+                if (d < dim) part = fmaf(qv[j], to_float(kp[d]), part);
+            }
+            const float s = warp_sum(part) * scale;
+            if (lane == k) mine = s;
+        }
+        if (talk != nullptr) {
+            __syncthreads();                    // the mixing of the chunk before has read `raw`
+            raw[h][lane] = mine;
+            __syncthreads();
+            float mixed = 0.f;
+            for (int g = 0; g < n_heads; ++g) mixed = fmaf(talk[h * n_heads + g], raw[g][lane], mixed);
+            mine = mixed;
+        }
+        if (lane >= nk) mine = -INFINITY;
+        const float m_new = fmaxf(m, warp_max(mine));
+        const float corr = expf(m - m_new);          // exp(-inf) = 0 at the first keys
+        const float pe_mine = lane < nk ? expf(mine - m_new) : 0.f;
+        float sum[kTalkMaxDim / 32];
+#pragma unroll
+        for (int j = 0; j < kTalkMaxDim / 32; ++j) sum[j] = 0.f;
+        float l_new = 0.f;
+        for (int k = 0; k < nk; ++k) {
+            const int p = p0 + k;
+            const T* vp = v_cache + (((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh) * v_dim;
+            const float pe = __shfl_sync(0xffffffffu, pe_mine, k);
+            l_new += pe;
+#pragma unroll
+            for (int j = 0; j < kTalkMaxDim / 32; ++j) {
+                const int d = lane + 32 * j;
+                if (d < v_dim) sum[j] = fmaf(pe, to_float(vp[d]), sum[j]);
+            }
+        }
+        l = l * corr + l_new;
+#pragma unroll
+        for (int j = 0; j < kTalkMaxDim / 32; ++j) acc[j] = acc[j] * corr + sum[j];
+        m = m_new;
+    }
+    float inv = 1.0f / l;
+    if (sinks != nullptr) {
+        const float sk = sinks[h];
+        const float m_all = fmaxf(m, sk);
+        const float corr = expf(m - m_all);
+        l = l * corr + expf(sk - m_all);
+        inv = corr / l;
+    }
+    T* op = out + ((size_t)t * n_heads + h) * v_dim;
+#pragma unroll
+    for (int j = 0; j < kTalkMaxDim / 32; ++j) {
+        const int d = lane + 32 * j;
+        if (d < v_dim) op[d] = from_float<T>(acc[j] * inv);
+    }
+}
+
+}  // namespace mdma
+
+using namespace mdma;
+
+extern "C" {
+
+int mdma_qk_norm_rotate(void* proj, int dtype, int row_stride, int k_col, int v_col, const int* tok_seq, const int* tok_pos,
+                        const int* seq_slot, const float* inv_freq, float magnitude, const void* q_w, const void* k_w,
+                        int w_dtype, int norm, float eps, void* k_cache, void* v_cache, const int* page_table,
+                        int max_pages, int page_size, int n_tokens, int n_heads, int n_kv_heads, int dim, int v_dim,
+                        int rotary_dim, int interleaved, int write_kv, cudaStream_t stream) {
+    MDMA_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads >= 0, "qk_norm_rotate: bad sizes");
+    MDMA_REQUIRE(dim > 0 && dim <= kTalkMaxDim && v_dim > 0, "qk_norm_rotate: head size %d is beyond the limit %d", dim, kTalkMaxDim);
+    MDMA_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dim, "qk_norm_rotate: rotary_dim %d does not fit head size %d", rotary_dim, dim);
+    MDMA_REQUIRE(rotary_dim == 0 || inv_freq, "qk_norm_rotate: a rotation needs its frequencies");
+    MDMA_REQUIRE(w_dtype == kF32 || w_dtype == kBF16, "qk_norm_rotate: unknown weight dtype %d", w_dtype);
+    MDMA_REQUIRE(!write_kv || (page_table && k_cache && v_cache && page_size > 0 && max_pages > 0), "qk_norm_rotate: no cache pages");
+    if (n_tokens == 0) return 0;
+    const int total = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    MDMA_DISPATCH_DTYPE(dtype, T,
+        launch_chained(qk_norm_rotate_kernel<T>, dim3(n_tokens, (total + kPrepWarpsT - 1) / kPrepWarpsT), dim3(kPrepWarpsT * 32),
+                       0, stream, (T*)proj, row_stride, k_col, v_col, tok_seq, tok_pos, seq_slot, inv_freq, magnitude, q_w, k_w,
+                       w_dtype, norm, eps, (T*)k_cache, (T*)v_cache, page_table, max_pages, page_size, n_heads, n_kv_heads,
+                       dim, v_dim, rotary_dim, interleaved, write_kv));
+    MDMA_LAUNCH_OK("qk_norm_rotate");
+    return 0;
+}
+
+int mdma_talking_attention(const void* q, int dtype, int q_row_stride, const void* k_cache, const void* v_cache,
+                           const float* talk, const float* sinks, const int* tok_seq, const int* tok_pos,
+                           const int* seq_slot, const int* page_table, int max_pages, int page_size, void* out,
+                           int n_tokens, int n_heads, int n_kv_heads, int dim, int v_dim, int window, float scale,
+                           cudaStream_t stream) {
+    MDMA_REQUIRE(n_heads > 0 && n_heads <= kTalkMaxHeads && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
+                 "talking_attention: %d heads over %d kv heads (at most %d heads)", n_heads, n_kv_heads, kTalkMaxHeads);
+    MDMA_REQUIRE(dim > 0 && dim <= kTalkMaxDim && v_dim > 0 && v_dim <= kTalkMaxDim,
+                 "talking_attention: head sizes %d/%d are beyond the limit %d", dim, v_dim, kTalkMaxDim);
+    MDMA_REQUIRE(page_table && page_size > 0 && max_pages > 0 && window >= 0, "talking_attention: bad cache geometry");
+    if (n_tokens == 0) return 0;
+    MDMA_DISPATCH_DTYPE(dtype, T,
+        launch_chained(talking_attention_kernel<T>, dim3(n_tokens), dim3(n_heads * 32), 0, stream, (const T*)q, q_row_stride,
+                       (const T*)k_cache, (const T*)v_cache, talk, sinks, tok_seq, tok_pos, seq_slot, page_table, max_pages,
+                       page_size, (T*)out, n_heads, n_kv_heads, dim, v_dim, window, scale));
+    MDMA_LAUNCH_OK("talking_attention");
+    return 0;
+}
+
+}  // extern "C"

@@ -28,7 +28,7 @@ static inline int fail(const char* fmt, ...) {
 }
 // What a matrix product adds on its way out: a vector over the output features (for the second matrix of
 // a gated product too), kept as float32 or bfloat16, and which activation a gated product applies to its gate.
-enum Activation : int { kActSilu = 0, kActGeluTanh = 1, kActGeluErf = 2, kActSwishLimit = 3 };
+enum Activation : int { kActSilu = 0, kActGeluTanh = 1, kActGeluErf = 2, kActSwishLimit = 3, kActReluSquared = 4 };
 struct Ending {
     const void* bias;     // [n_features] or null
     const void* bias2;    // the second matrix's, or null
@@ -46,12 +46,14 @@ __device__ __forceinline__ float ending_bias(const void* b, int dtype, int f) {
 __device__ __forceinline__ float gate_activation(float g, int act) {
     if (act == kActGeluTanh) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     if (act == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
+    if (act == kActReluSquared) { const float r = fmaxf(g, 0.f); return r * r; }
     return g / (1.0f + expf(-g));
 }
 // ... and with the fast exponential (the bfloat16 engine): 0.5 (1 + tanh t) = 1 / (1 + e^(-2t)).
 __device__ __forceinline__ float gate_activation_fast(float g, int act) {
     if (act == kActGeluTanh) return g / (1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
     if (act == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
+    if (act == kActReluSquared) { const float r = fmaxf(g, 0.f); return r * r; }
     return g / (1.0f + __expf(-g));
 }
 // What a gated feed-forward makes of its two products g and u: act(g) * u, or, for kActSwishLimit,

@@ -137,7 +137,7 @@ extern "C" int mdma_gemm_simt(int mode, const void* A, int a_dtype, int lda, con
     MDMA_REQUIRE(mode != kSwiGLU || W2 != nullptr, "gemm_simt: SwiGLU needs two weights");
     MDMA_REQUIRE(mode != kAccumulate || out_dtype == kF32, "gemm_simt: the residual stream is float");
     MDMA_REQUIRE((size_t)((M + TM - 1) / TM) <= 65535, "gemm_simt: too many rows (%d)", M);
-    MDMA_REQUIRE(act >= kActSilu && act <= kActSwishLimit, "gemm_simt: unknown activation %d", act);
+    MDMA_REQUIRE(act >= kActSilu && act <= kActReluSquared, "gemm_simt: unknown activation %d", act);
     MDMA_REQUIRE(act != kActSwishLimit || mode == kSwiGLU, "gemm_simt: the limited activation belongs to a gated product");
     MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_simt: unknown bias dtype %d", bias_dtype);
     if (M == 0) return 0;

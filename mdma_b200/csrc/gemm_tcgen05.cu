@@ -918,7 +918,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!w2 || ((uintptr_t)w2 & 15) == 0),
                  "gemm_tc: operands must be 16-byte aligned");
     MDMA_REQUIRE(mode != kTcSwiGLU || w2, "gemm_tc: SwiGLU needs two weights");
-    MDMA_REQUIRE(act >= kActSilu && act <= kActSwishLimit, "gemm_tc: unknown activation %d", act);
+    MDMA_REQUIRE(act >= kActSilu && act <= kActReluSquared, "gemm_tc: unknown activation %d", act);
     MDMA_REQUIRE(act != kActSwishLimit || mode == kTcSwiGLU, "gemm_tc: the limited activation belongs to a gated product");
     MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_tc: unknown bias dtype %d", bias_dtype);
     const Ending ending{bias, mode == kTcSwiGLU ? bias2 : nullptr, bias_dtype, act, store_act, act_limit, act_alpha};

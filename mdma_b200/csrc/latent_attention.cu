@@ -4,7 +4,7 @@
 // (q' = W_uk,h^T q_h, `rank` numbers per head) the score is q' . c, and with the values' map
 // applied after the weighted sum (o_h = W_uv,h sum_j p_j c_j) the cache is read as one shared
 // key-and-value head of size `rank`.  The softmax has a sink: exp(sink_h) is added to the
-// denominator once, with no key, no value and no scale.
+// denominator once, with no key, no value and no scale (no sink pointer: the ordinary softmax).
 //
 // Plain kernels: one warp per (token, head), keys visited in position order, 32 at a time
 // (their scores first, then their maximum, then their weighted sum from zero, which is
@@ -110,11 +110,14 @@ latent_attention_kernel(const T* __restrict__ q, int q_row_stride, const T* __re
         for (int j = 0; j < kMaxRank / 32; ++j) acc[j] = acc[j] * corr + sum[j];
         m = m_new;
     }
-    const float sk = to_float(sink[h]);
-    const float m_all = fmaxf(m, sk);
-    const float corr = expf(m - m_all);
-    l = l * corr + expf(sk - m_all);
-    const float inv = corr / l;
+    float inv = 1.0f / l;                       // no sink: the ordinary softmax
+    if (sink != nullptr) {
+        const float sk = to_float(sink[h]);
+        const float m_all = fmaxf(m, sk);
+        const float corr = expf(m - m_all);
+        l = l * corr + expf(sk - m_all);
+        inv = corr / l;
+    }
     T* op = out + ((size_t)t * n_heads + h) * rank;
 #pragma unroll
     for (int j = 0; j < kMaxRank / 32; ++j) {

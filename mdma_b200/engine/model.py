@@ -33,8 +33,9 @@ class DecoderModel:
         # called as on_layer(n, x) after the n-th run of the schedule with the residual rows (a debugging aid)
         self.on_layer = None
         for n, entry in enumerate(spec.schedule):
-            if entry.junction is not None and not 0 <= entry.junction < len(self.junctions):
-                raise ValueError(f"schedule entry {n} names junction {entry.junction}, there are {len(self.junctions)}")
+            for j in (entry.junction, entry.after):
+                if j is not None and not 0 <= j < len(self.junctions):
+                    raise ValueError(f"schedule entry {n} names junction {j}, there are {len(self.junctions)}")
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {n} names layer {entry.layer}, there are {len(self.blocks)}")
             if entry.cache is not None:
@@ -177,6 +178,11 @@ class DecoderModel:
                 from .. import ops_tensor
                 ops_tensor.flush_pending(x.device, ctx.rt.tc)
             block.forward(ctx, x, cache.view(site, state_site=n), owns_cache=entry.cache is None)
+            if entry.after is not None:
+                if ctx.rt.gemm == "tensor":
+                    from .. import ops_tensor
+                    ops_tensor.flush_pending(x.device, ctx.rt.tc)
+                self.junctions[entry.after].forward(ctx, x, x0, n)
             if self.on_layer is not None:
                 if ctx.rt.gemm == "tensor":
                     from .. import ops_tensor

@@ -104,10 +104,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
           ctypes.c_long(split_stride), _stream())
 
 
-ACT_SILU, ACT_GELU_TANH, ACT_GELU, ACT_SWISH_LIMIT = 0, 1, 2, 3
+ACT_SILU, ACT_GELU_TANH, ACT_GELU, ACT_SWISH_LIMIT, ACT_RELU_SQUARED = 0, 1, 2, 3, 4
 # "gelu" is the exact one, 0.5 z (1 + erf(z / sqrt 2)).  "swish_limit" belongs to gated products only: with the gate's
 # product g cut off above `limit` and the other product u kept within +-limit, g sigmoid(alpha g) (u + 1).
-ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU, "swish_limit": ACT_SWISH_LIMIT}
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU, "swish_limit": ACT_SWISH_LIMIT,
+               "relu_squared": ACT_RELU_SQUARED}
 
 
 def ending_args(n_features: int, bias: Optional[torch.Tensor], bias2: Optional[torch.Tensor], act: int,
@@ -443,12 +444,12 @@ def latent_norm_store(proj, col0: int, w, eps: float, rank: int, tok_seq, tok_po
 def latent_attention(q, cache, sink, tok_seq, tok_pos, seq_slot, page_table, max_pages: int, page_size: int, out,
                      n_tokens: int, n_heads: int, rank: int, window: int, scale: float) -> None:
     """q [T, heads*rank]: queries already mapped into the latent; out [T, heads*rank]: the weighted sums of
-    cached latents, softmax with one sink term per head in the denominator."""
+    cached latents, softmax with one sink term per head in the denominator (`sink` None: none)."""
     _need_cuda(q, cache, sink, tok_seq, tok_pos, seq_slot, page_table, out)
     assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == cache.dtype and cache.is_contiguous()
-    assert out.shape[1] == n_heads * rank and sink.numel() == n_heads and sink.is_contiguous()
+    assert out.shape[1] == n_heads * rank and (sink is None or (sink.numel() == n_heads and sink.is_contiguous()))
     _call("core", "mdma_latent_attention", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(cache), _ptr(sink),
-          _i(dtype_code(sink.dtype)), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
+          _i(dtype_code(sink.dtype) if sink is not None else F32), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
           _i(page_size), _ptr(out), _i(n_tokens), _i(n_heads), _i(rank), _i(window), _f(scale), _stream())
 
 
@@ -702,3 +703,112 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: tor
     assert gate.stride(1) == 1 and gate.shape[1] >= width and w.numel() == width and w.is_contiguous()
     _call("core", "mdma_gated_rmsnorm", _ptr(o), _ptr(gate), _i(dtype_code(gate.dtype)), _i(gate.stride(0)), _ptr(w),
           _i(dtype_code(w.dtype)), _ptr(out), _i(dtype_code(out.dtype)), _i(n_rows), _i(width), _f(eps), _f(scale), _stream())
+
+
+# ---- RMS norm in groups, the weighted sum over the depth (csrc/group_norm.cu) ----------------------------------------
+def group_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, groups: int, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+    """out[i] = the row x[rows[i]] (or x[i]) in `groups` equal parts, each divided by its own root mean square, times w."""
+    _need_cuda(x, w, out, rows)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    width = x.shape[-1]
+    assert w.numel() == width and out.shape[-1] == width and w.is_contiguous()
+    n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert out.shape[0] >= n and (rows is None or rows.dtype == torch.int32)
+    _call("core", "mdma_group_rmsnorm", _ptr(x), _ptr(w), _i(dtype_code(w.dtype)), _ptr(rows), _ptr(out),
+          _i(dtype_code(out.dtype)), _i(n), _i(width), _i(groups), _f(eps), _stream())
+
+
+def group_rmsnorm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, groups: int, n_rows: int,
+                      partial: Optional[torch.Tensor] = None, splits: int = 0, split_stride: int = 0) -> None:
+    """x[t] += group norm of y[t] times w; x and y float rows.  With `partial` [splits, rows, width], y is first
+    completed by those sums (a K-split product not yet added up)."""
+    _need_cuda(x, y, w, partial)
+    width = x.shape[1]
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape[1] == width
+    assert w.numel() == width and w.is_contiguous()
+    _call("core", "mdma_group_rmsnorm_add", _ptr(x), _ptr(y), _ptr(partial), _i(splits if partial is not None else 0),
+          ctypes.c_long(split_stride), _ptr(w), _i(dtype_code(w.dtype)), _i(n_rows), _i(width), _i(groups), _f(eps), _stream())
+
+
+def depth_mix(x: torch.Tensor, x0: torch.Tensor, history: torch.Tensor, depth: int, run: int, w: torch.Tensor,
+              n_rows: int) -> None:
+    """history[t, run] = x[t]; x[t] = w[0] x0[t] + sum_{j<=run} w[j+1] history[t, j].  Float rows; history
+    [rows, depth * width]."""
+    _need_cuda(x, x0, history, w)
+    width = x.shape[1]
+    assert x.dtype == x0.dtype == history.dtype == torch.float32 and x.is_contiguous() and x0.is_contiguous()
+    assert history.is_contiguous() and history.shape[1] == depth * width and w.numel() >= run + 2 and w.is_contiguous()
+    _call("core", "mdma_depth_mix", _ptr(x), _ptr(x0), _ptr(history), _i(depth), _i(run), _ptr(w), _i(dtype_code(w.dtype)),
+          _i(n_rows), _i(width), _stream())
+
+
+# ---- a cached latent with a turned key part (csrc/rotary_latent.cu) ----------------------------------------------------
+def latent_prepare(proj, q_col: int, q_rank: int, q_w, kv_col: int, kv_rank: int, kv_w, eps: float, rot_dim: int,
+                   rotary_dim: int, interleaved: bool, inv_freq, magnitude: float, tok_seq, tok_pos, seq_slot, page_table,
+                   max_pages: int, page_size: int, cq, cache, write_cache: bool, n_tokens: int) -> None:
+    """cq[t] = rms_unit(proj[t, q_col:+q_rank]) * q_w; with `write_cache`, the token's cache row becomes
+    [rms_unit(proj[t, kv_col:+kv_rank]) * kv_w | the next rot_dim numbers, turned by the token's position]."""
+    _need_cuda(proj, q_w, kv_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, cq, cache)
+    assert proj.stride(1) == 1 and cq.is_contiguous() and cq.dtype == proj.dtype and cq.shape[1] == q_rank
+    assert q_w.numel() == q_rank and q_w.is_contiguous()
+    w_dtype = dtype_code(q_w.dtype)
+    if write_cache:
+        assert cache.is_contiguous() and cache.dtype == proj.dtype and cache.shape[-1] == kv_rank + rot_dim
+        assert kv_w.numel() == kv_rank and kv_w.dtype == q_w.dtype and kv_w.is_contiguous()
+        assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
+    _call("core", "mdma_latent_prepare", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(q_col), _i(q_rank),
+          _ptr(q_w), _i(kv_col), _i(kv_rank), _ptr(kv_w), _i(w_dtype), _f(eps), _i(rot_dim), _i(rotary_dim),
+          _i(int(interleaved)), _ptr(inv_freq), _f(magnitude), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table),
+          _i(max_pages), _i(page_size), _ptr(cq), _ptr(cache), _i(int(write_cache)), _i(n_tokens), _stream())
+
+
+def rotate_heads(q, n_heads: int, head_pitch: int, offset: int, rotary_dim: int, interleaved: bool, inv_freq,
+                 magnitude: float, tok_pos, n_tokens: int) -> None:
+    """Columns [offset, offset + rotary_dim) of every head of q [tokens, heads * head_pitch] turned in place."""
+    _need_cuda(q, inv_freq, tok_pos)
+    assert q.stride(1) == 1 and q.shape[1] >= n_heads * head_pitch
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
+    _call("core", "mdma_rotate_heads", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _i(n_heads), _i(head_pitch),
+          _i(offset), _i(rotary_dim), _i(int(interleaved)), _ptr(inv_freq), _f(magnitude), _ptr(tok_pos), _i(n_tokens), _stream())
+
+
+# ---- attention whose heads' scores are mixed before the softmax (csrc/attention_talking.cu) --------------------------
+def qk_norm_rotate(proj, k_col: int, v_col: int, tok_seq, tok_pos, seq_slot, inv_freq, magnitude: float, q_w, k_w,
+                   norm: bool, eps: float, k_cache, v_cache, page_table, max_pages: int, page_size: int, n_tokens: int,
+                   n_heads: int, n_kv_heads: int, dim: int, v_dim: int, rotary_dim: int, interleaved: bool,
+                   write_kv: bool) -> None:
+    """Rows [q heads | k heads at k_col | v heads at v_col]: q and k heads are (with `norm`) divided by their root mean
+    square and multiplied by q_w / k_w [dim], then their first `rotary_dim` numbers are turned by the token's position;
+    q in place, k and v to the token's cache row (`write_kv`)."""
+    _need_cuda(proj, tok_seq, tok_pos, seq_slot, inv_freq, q_w, k_w, k_cache, v_cache, page_table)
+    assert proj.stride(1) == 1 and (inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2))
+    w_dtype = F32
+    if q_w is not None:
+        assert q_w.numel() == dim and k_w.numel() == dim and q_w.dtype == k_w.dtype and q_w.is_contiguous() and k_w.is_contiguous()
+        w_dtype = dtype_code(q_w.dtype)
+    if write_kv:
+        assert k_cache.dtype == proj.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[-1] == dim and v_cache.shape[-1] == v_dim
+        assert proj.shape[1] >= v_col + n_kv_heads * v_dim and v_col >= k_col + n_kv_heads * dim >= 0
+    _call("core", "mdma_qk_norm_rotate", _ptr(proj), _i(dtype_code(proj.dtype)), _i(proj.stride(0)), _i(k_col), _i(v_col),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(inv_freq), _f(magnitude), _ptr(q_w), _ptr(k_w), _i(w_dtype),
+          _i(int(norm)), _f(eps), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _i(max_pages), _i(page_size), _i(n_tokens),
+          _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(rotary_dim), _i(int(interleaved)), _i(int(write_kv)), _stream())
+
+
+def talking_attention(q, k_cache, v_cache, talk, sinks, tok_seq, tok_pos, seq_slot, page_table, max_pages: int,
+                      page_size: int, out, n_tokens: int, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int,
+                      scale: float) -> None:
+    """out[t, h] = sum_j p_hj v_j with p_h the softmax over the keys up to the token's position of the MIXED scores
+    sum_g talk[h, g] (q_g . k_j) scale; `sinks` [heads] float join each denominator as exp(sink_h); `talk` None: heads
+    on their own."""
+    _need_cuda(q, k_cache, v_cache, talk, sinks, tok_seq, tok_pos, seq_slot, page_table, out)
+    assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == k_cache.dtype == v_cache.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and out.shape[1] == n_heads * v_dim
+    assert talk is None or (talk.dtype == torch.float32 and talk.is_contiguous() and talk.numel() == n_heads * n_heads)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads)
+    _call("core", "mdma_talking_attention", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(k_cache), _ptr(v_cache),
+          _ptr(talk), _ptr(sinks), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
+          _i(page_size), _ptr(out), _i(n_tokens), _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale),
+          _stream())

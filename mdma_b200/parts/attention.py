@@ -51,6 +51,8 @@ class Attention(Part):
             raise ValueError(f"{self.n_heads} heads do not divide over {self.n_kv_heads} kv heads")
         pos = p.get("position")
         self.position = POSITIONS.get(pos.kind)(pos) if pos is not None else None
+        if getattr(self.position, "magnitude", 1.0) != 1.0:
+            raise ValueError("this attention part takes rotations without a factor on cos and sin")
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv_heads * self.head_dim
         self.row_width = self.q_width + (0 if self.shared_cache else 2 * self.kv_width)

@@ -13,6 +13,10 @@ x0 the embedding's output and s_t a learned vector per pass.
 
 Loop add: the same place, without a matrix: x <- x + x0 (not before the first
 pass), then x <- x + s_t.
+
+Depth average: AFTER run i of the schedule, what goes on is a learned weighted
+sum of the embedding's output X_0 and the results X_1 .. X_(i+1) of all runs so
+far, x <- sum_j w[j] X_j; X_(i+1) is the run's result before this sum.
 """
 from __future__ import annotations
 
@@ -145,3 +149,36 @@ class LoopAdd(Part):
 
     def resident_tensors(self):
         return [self.step]
+
+
+@JUNCTIONS.register("depth_average")
+class DepthAverage(Part):
+    """After run `arg` of the schedule: x <- sum_{j=0..arg+1} w[j] X_j, with X_0 the embedding's output and X_(j+1)
+    the result of run j as that run left it (before its own average).  `terms` = arg + 2 weights; `depth` = runs in the
+    schedule, which sizes the per-token history [depth, width] of float rows.  Sums in float, terms in the order of j."""
+    needs_embedding = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width, self.terms, self.depth = int(self.params["width"]), int(self.params["terms"]), int(self.params["depth"])
+        if not 2 <= self.terms <= self.depth + 1:
+            raise ValueError(f"a depth average of {self.terms} terms in a schedule of {self.depth} runs")
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.terms,), "vector", "normal")}
+
+    def workspace(self):
+        return {f"depth_history_{self.depth}": (self.depth * self.width, "f32")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors["weight"]
+
+    def forward(self, ctx, x, x0, run: int):
+        if run + 2 != self.terms:
+            raise ValueError(f"a depth average of {self.terms} terms was placed after run {run}")
+        history = ctx.buf(f"depth_history_{self.depth}", self.depth * self.width, torch.float32)
+        ops.depth_mix(x, x0, history, self.depth, run, self.weight, ctx.n_tokens)
+
+    def resident_tensors(self):
+        return [self.weight]

@@ -3,6 +3,8 @@
 RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w (src/backend/cpu.rs:388-401;
 no +1 on the weight, no mean subtraction); sums in float.  `add_normed` is the
 same norm on a sublayer's result, added into the residual stream: x += norm(y).
+With `groups` g > 1 the row is split into g equal consecutive parts and every part is divided
+by its own sqrt(mean(part^2) + eps); the weight spans the whole row.
 
 Dynamic tanh: y = tanh(alpha * x) * w + b with a learned scalar alpha; no mean,
 no variance, nothing summed over the row.
@@ -23,6 +25,11 @@ class RMSNorm(Part):
         super().__init__(spec)
         self.width = int(self.params["width"])
         self.eps = float(self.params["eps"])
+        self.groups = int(self.params.get("groups", 1) or 1)
+        if self.groups < 1 or self.width % self.groups:
+            raise ValueError(f"a row of {self.width} numbers does not split into {self.groups} equal parts")
+        if self.groups > 1:
+            self.fuses_pending = False      # the grouped kernel reads complete rows of x
 
     def tensor_specs(self):
         return {"weight": TensorSpec((self.width,), "vector")}
@@ -35,6 +42,12 @@ class RMSNorm(Part):
 
     def forward(self, ctx, x, out, rows=None, n_rows=None):
         n = n_rows if n_rows is not None else (None if rows is not None else ctx.n_tokens)
+        if self.groups > 1:
+            if self.rt.gemm == "tensor":
+                from .. import ops_tensor
+                ops_tensor.flush_pending(x.device, self.rt.tc)
+            ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out, rows, n)
+            return
         if self.rt.gemm == "tensor":
             from .. import ops_tensor
             pend = ops_tensor.take_pending(x, ops.GEMM_ACCUMULATE, ctx.n_tokens, self.rt.tc) if rows is None else None
@@ -56,6 +69,9 @@ class RMSNorm(Part):
                 partial, splits, stride = pend
             else:
                 ops_tensor.flush_pending(y.device, self.rt.tc)
+        if self.groups > 1:
+            ops.group_rmsnorm_add(x, y, self.weight, self.eps, self.groups, ctx.n_tokens, partial, splits, stride)
+            return
         ops.rmsnorm_add(x, y, self.weight, self.eps, ctx.n_tokens, partial, splits, stride)
 
     def resident_tensors(self):

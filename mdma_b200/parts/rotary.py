@@ -10,6 +10,13 @@ builds it on the host too: src/backend/cuda.rs:383-398); llama3 scaling
 divides each frequency by a factor chosen by its wavelength.  Rotated keys are
 written straight into the cache, so the encoding is fixed at write time
 (src/model/arch/llama.rs:198-209).
+
+A second kind of scaling, a dict {kind: "ramp", factor, original, fast, slow, magnitude_slope}: with
+turn(t) = d ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(turn(fast)), 0), hi = min(ceil(turn(slow)), d - 1)
+and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i (1 - ramp_i),
+and cos and sin are both multiplied by `magnitude` = magnitude_slope * ln(factor) + 1.  Kernels that take a
+frequency table alone cannot apply the magnitude; `encode_and_store` refuses it, mixers that can take it read
+`magnitude`.
 """
 from __future__ import annotations
 
@@ -25,6 +32,21 @@ from .base import Part
 def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor:
     """float32 [rotary_dim/2]."""
     out = []
+    if isinstance(scaling, dict):
+        if scaling.get("kind") != "ramp":
+            raise ValueError(f"unknown rotary scaling {scaling.get('kind')!r}")
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def turn(t: float) -> float:
+            return rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(float(theta)))
+
+        lo = max(math.floor(turn(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(turn(float(scaling["slow"]))), rotary_dim - 1)
+        for i in range(rotary_dim // 2):
+            f = float(theta) ** (-2.0 * i / rotary_dim)
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * ramp + f * (1.0 - ramp))
+        return torch.tensor(out, dtype=torch.float64).to(torch.float32)
     for i in range(rotary_dim // 2):
         f = float(theta) ** (-2.0 * i / rotary_dim)
         if scaling is not None:
@@ -55,6 +77,10 @@ class Rotary(Part):
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.table_host = inverse_frequencies(self.rotary_dim, p["theta"], p.get("scaling"))
+        scaling = p.get("scaling")
+        self.magnitude = 1.0         # a factor on cos and sin (the "ramp" scaling sets it)
+        if isinstance(scaling, dict):
+            self.magnitude = float(scaling.get("magnitude_slope", 0.0)) * math.log(float(scaling["factor"])) + 1.0
 
     def bind(self, tensors, rt):
         if getattr(self, "rt", None) is rt and getattr(self, "inv_freq", None) is not None:
@@ -76,6 +102,8 @@ class Rotary(Part):
         return self.inv_freq, self.rotary_dim, self.interleaved
 
     def encode_and_store(self, ctx, qkv, n_heads, n_kv_heads, head_dim, view, write_kv):
+        if self.magnitude != 1.0:
+            raise ValueError("this rotation multiplies cos and sin by a factor; the kernel behind encode_and_store has none")
         partial, splits, stride = None, 0, 0
         if self.rt.gemm == "tensor":
             from .. import ops_tensor

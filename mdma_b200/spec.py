@@ -63,6 +63,8 @@ class ScheduleEntry:
     # this run, and the number it is given (which pass of a loop begins here)
     junction: Optional[int] = None
     junction_arg: int = 0
+    # a junction that acts on the residual stream right after this run (it is given the run's number in the schedule)
+    after: Optional[int] = None
 
 
 @dataclass
