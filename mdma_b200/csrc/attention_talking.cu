@@ -16,9 +16,13 @@
 // weighted value sum).  Everything in float in one fixed order: the result of a token does not depend on the
 // step's cut or on the batch.
 //
-// Tiled kernel: a block takes 16 consecutive rows of one sequence and all heads; keys and values of a kv head are
-// staged 32 keys at a time in shared memory as float, raw scores of all heads for the 16 x 32 tile are kept in shared
-// memory, mixed, and folded row by row.  Steps of many rows in the serving engine.
+// Tiled kernel: a block takes up to eight consecutive rows of one sequence and ALL heads (the mixing needs every
+// head's score of a key).  Keys are walked 32 at a time.  For every kv head in turn the chunk's keys are staged in
+// shared memory as float and the raw scores of its query heads are computed, a lane per key, up to four heads on
+// one read of a key; then a warp per (row, head) mixes the raw scores of all heads, applies the mask, and folds the
+// chunk into the running maximum and normaliser, leaving the chunk's weights in shared memory; then, for every kv
+// head in turn, the chunk's values are staged and the weighted sums are folded into the running sums, lanes over the
+// value columns.  The serving engine's kernel: sums in another order than the plain one, rounding only.
 #include "common.cuh"
 
 namespace mdma {
@@ -184,6 +188,190 @@ talking_attention_kernel(const T* __restrict__ q, int q_row_stride, const T* __r
     }
 }
 
+// ---------------------------------------------------------------- tiled kernel
+constexpr int kTalkChunk = 32, kTalkWarps = 8, kTalkTogether = 4, kTalkMaxRows = 8;
+
+__device__ __forceinline__ void talk_stage8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void talk_stage8(const __nv_bfloat16* p, float* v) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+}
+
+// rows [chunk keys][width] of kv head `kvh` into shared memory as float, row pitch `pitch`
+template <typename T>
+__device__ __forceinline__ void talk_stage(const T* __restrict__ cache, const int* __restrict__ pages, int page_size,
+                                           int n_kv_heads, int kvh, int width, int c0, int n_keys, float* dst, int pitch) {
+    constexpr int kPerKey = kTalkWarps * 32 / kTalkChunk;
+    const int j = threadIdx.x / kPerKey, part = threadIdx.x % kPerKey;
+    if (j >= n_keys) return;
+    const int p = c0 + j;
+    const T* src = cache + (((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh) * width;
+    float* row = dst + (size_t)j * pitch;
+    if (width % 8 == 0 && ((uintptr_t)cache & 15) == 0) {
+        for (int d = part * 8; d < width; d += kPerKey * 8) {
+            float t8[8];
+            talk_stage8(src + d, t8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) row[d + i] = t8[i];
+        }
+    } else {
+        for (int d = part; d < width; d += kPerKey) row[d] = to_float(src[d]);
+    }
+}
+
+static size_t talk_tiled_smem(int rows, int n_heads, int dim, int v_dim) {
+    const size_t pairs = (size_t)rows * n_heads;
+    const size_t stage = (size_t)kTalkChunk * (size_t)((dim + 1) > v_dim ? (dim + 1) : v_dim);
+    return (pairs * dim + pairs * v_dim + stage + 2 * pairs * kTalkChunk + 3 * pairs) * sizeof(float);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTalkWarps * 32)
+talking_attention_tiled_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_cache,
+                               const T* __restrict__ v_cache, const float* __restrict__ talk, const float* __restrict__ sinks,
+                               const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
+                               const int* __restrict__ seq_slot, const int* __restrict__ page_table, int max_pages,
+                               int page_size, T* __restrict__ out, int n_heads, int n_kv_heads, int dim, int v_dim,
+                               int window, float scale, int tile_rows) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float smem[];
+    const int s = blockIdx.y;
+    const int t0 = seq_start[s], n_new = seq_start[s + 1] - t0;
+    const int r0 = blockIdx.x * tile_rows;
+    if (r0 >= n_new) return;
+    const int rows = min(tile_rows, n_new - r0);
+    const int group = n_heads / n_kv_heads;
+    const int pos0 = seq_pos0[s] + r0;                     // position of the tile's first row
+    const int last = pos0 + rows - 1;
+    const int first = window > 0 ? max(0, pos0 + 1 - window) : 0;
+    const int* pages = page_table + (size_t)seq_slot[s] * max_pages;
+    const int kd = dim + 1;                                // padded key rows: lanes read different keys
+    const int pairs = tile_rows * n_heads;                 // (head, row) pairs, head-major: pair = h * tile_rows + r
+    float* sq = smem;                                      // [pairs][dim]
+    float* so = sq + (size_t)pairs * dim;                  // [pairs][v_dim] running sums
+    float* st = so + (size_t)pairs * v_dim;                // [chunk][dim + 1] keys or [chunk][v_dim] values
+    float* raw = st + (size_t)kTalkChunk * max(kd, v_dim); // [pairs][chunk] raw scores
+    float* sp = raw + (size_t)pairs * kTalkChunk;          // [pairs][chunk] weights of the chunk
+    float* sm = sp + (size_t)pairs * kTalkChunk;           // [pairs] running maximum
+    float* sl = sm + pairs;                                // [pairs] normaliser
+    float* sc = sl + pairs;                                // [pairs] this chunk's correction of the running sums
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    for (int e = threadIdx.x; e < n_heads * rows * dim; e += blockDim.x) {
+        const int h = e / (rows * dim), r = (e / dim) % rows, d = e % dim;
+        sq[(size_t)(h * tile_rows + r) * dim + d] = to_float(q[(size_t)(t0 + r0 + r) * q_row_stride + (size_t)h * dim + d]);
+    }
+    for (int e = threadIdx.x; e < pairs * v_dim; e += blockDim.x) so[e] = 0.f;
+    for (int e = threadIdx.x; e < pairs; e += blockDim.x) { sm[e] = -INFINITY; sl[e] = 0.f; }
+
+    for (int c0 = first; c0 <= last; c0 += kTalkChunk) {
+        const int n_keys = min(kTalkChunk, last + 1 - c0);
+        // raw scores, kv head by kv head
+        for (int kvh = 0; kvh < n_kv_heads; ++kvh) {
+            __syncthreads();                               // the staging buffer is free (and q is in place)
+            talk_stage(k_cache, pages, page_size, n_kv_heads, kvh, dim, c0, n_keys, st, kd);
+            __syncthreads();
+            const int head_chunks = (group + kTalkTogether - 1) / kTalkTogether;
+            for (int unit = warp; unit < rows * head_chunks; unit += kTalkWarps) {
+                const int r = unit / head_chunks, g0 = (unit % head_chunks) * kTalkTogether;
+                const int ng = min(kTalkTogether, group - g0);
+                const int h0 = kvh * group + g0;
+                float a[kTalkTogether];
+#pragma unroll
+                for (int g = 0; g < kTalkTogether; ++g) a[g] = 0.f;
+                if (lane < n_keys) {
+                    const float* kp = st + lane * kd;
+                    const float* qp = sq + (size_t)(h0 * tile_rows + r) * dim;
+                    for (int d = 0; d < dim; ++d) {
+                        const float kv = kp[d];
+#pragma unroll
+                        for (int g = 0; g < kTalkTogether; ++g)
+                            if (g < ng) a[g] = fmaf(qp[(size_t)g * tile_rows * dim + d], kv, a[g]);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < kTalkTogether; ++g)
+                    if (g < ng) raw[(size_t)((h0 + g) * tile_rows + r) * kTalkChunk + lane] = a[g] * scale;
+            }
+        }
+        __syncthreads();
+        // mix, mask, fold into the running maximum and normaliser; the chunk's weights stay in `sp`
+        for (int unit = warp; unit < rows * n_heads; unit += kTalkWarps) {
+            const int h = unit / rows, r = unit % rows;
+            const int pr = h * tile_rows + r;
+            const int pos = pos0 + r, p = c0 + lane;
+            const int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+            float mixed;
+            if (talk != nullptr) {
+                mixed = 0.f;
+                for (int g = 0; g < n_heads; ++g)
+                    mixed = fmaf(talk[h * n_heads + g], raw[(size_t)(g * tile_rows + r) * kTalkChunk + lane], mixed);
+            } else {
+                mixed = raw[(size_t)pr * kTalkChunk + lane];
+            }
+            const bool seen = lane < n_keys && p <= pos && p >= lo;
+            const float score = seen ? mixed : -INFINITY;
+            const float cmax = warp_max(score);
+            const bool live = cmax != -INFINITY;           // else none of the chunk's keys is visible to this row
+            const float m_old = sm[pr];
+            const float m_new = live ? fmaxf(m_old, cmax) : m_old;
+            const float corr = live ? expf(m_old - m_new) : 1.f;
+            const float pe = seen ? expf(score - m_new) : 0.f;
+            sp[(size_t)pr * kTalkChunk + lane] = pe;
+            const float lsum = warp_sum(pe);
+            if (lane == 0) { sm[pr] = m_new; sl[pr] = sl[pr] * corr + lsum; sc[pr] = corr; }
+        }
+        // weighted sums over the chunk's values, kv head by kv head
+        for (int kvh = 0; kvh < n_kv_heads; ++kvh) {
+            __syncthreads();                               // weights are written; the staging buffer is free
+            talk_stage(v_cache, pages, page_size, n_kv_heads, kvh, v_dim, c0, n_keys, st, v_dim);
+            __syncthreads();
+            const int head_chunks = (group + kTalkTogether - 1) / kTalkTogether;
+            for (int unit = warp; unit < rows * head_chunks; unit += kTalkWarps) {
+                const int r = unit / head_chunks, g0 = (unit % head_chunks) * kTalkTogether;
+                const int ng = min(kTalkTogether, group - g0);
+                const int pr0 = (kvh * group + g0) * tile_rows + r;
+                for (int d = lane; d < v_dim; d += 32) {
+                    float a[kTalkTogether];
+#pragma unroll
+                    for (int g = 0; g < kTalkTogether; ++g)
+                        a[g] = (g < ng) ? so[(size_t)(pr0 + g * tile_rows) * v_dim + d] * sc[pr0 + g * tile_rows] : 0.f;
+                    for (int j = 0; j < n_keys; ++j) {
+                        const float v = st[j * v_dim + d];
+#pragma unroll
+                        for (int g = 0; g < kTalkTogether; ++g)
+                            if (g < ng) a[g] = fmaf(sp[(size_t)(pr0 + g * tile_rows) * kTalkChunk + j], v, a[g]);
+                    }
+#pragma unroll
+                    for (int g = 0; g < kTalkTogether; ++g)
+                        if (g < ng) so[(size_t)(pr0 + g * tile_rows) * v_dim + d] = a[g];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_heads * rows * v_dim; e += blockDim.x) {
+        const int h = e / (rows * v_dim), r = (e / v_dim) % rows, d = e % v_dim;
+        const int pr = h * tile_rows + r;
+        float o = so[(size_t)pr * v_dim + d], l = sl[pr];
+        if (sinks) {
+            const float sink = sinks[h], m = sm[pr];
+            if (sink > m) { const float c = expf(m - sink); o *= c; l = l * c + 1.0f; }
+            else l += expf(sink - m);
+        }
+        out[((size_t)(t0 + r0 + r) * n_heads + h) * v_dim + d] = from_float<T>(o / l);
+    }
+}
+
 }  // namespace mdma
 
 using namespace mdma;
@@ -209,6 +397,43 @@ int mdma_qk_norm_rotate(void* proj, int dtype, int row_stride, int k_col, int v_
                        w_dtype, norm, eps, (T*)k_cache, (T*)v_cache, page_table, max_pages, page_size, n_heads, n_kv_heads,
                        dim, v_dim, rotary_dim, interleaved, write_kv));
     MDMA_LAUNCH_OK("qk_norm_rotate");
+    return 0;
+}
+
+// Rows a tile of the tiled kernel can take for this geometry within its shared memory (8, 4, 2, 1), or 0.
+int mdma_talking_attention_tile_rows(int n_heads, int n_kv_heads, int dim, int v_dim, int most_rows) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || dim <= 0 || v_dim <= 0) return 0;
+    for (int rows = kTalkMaxRows; rows >= 1; rows >>= 1) {
+        if (rows > 1 && rows / 2 >= most_rows) continue;          // a smaller tile holds every row a sequence brings
+        if (talk_tiled_smem(rows, n_heads, dim, v_dim) <= 200 * 1024) return rows;
+    }
+    return 0;
+}
+
+int mdma_talking_attention_tiled(const void* q, int dtype, int q_row_stride, const void* k_cache, const void* v_cache,
+                                 const float* talk, const float* sinks, const int* seq_start, const int* seq_pos0,
+                                 const int* seq_slot, const int* page_table, int max_pages, int page_size, void* out,
+                                 int n_tokens, int n_seqs, int max_new, int n_heads, int n_kv_heads, int dim, int v_dim,
+                                 int window, float scale, cudaStream_t stream) {
+    MDMA_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && dim > 0 && v_dim > 0, "talking_attention: bad sizes");
+    MDMA_REQUIRE(page_table && page_size > 0 && max_pages > 0 && window >= 0 && seq_start && seq_pos0, "talking_attention: bad cache geometry");
+    if (n_tokens == 0 || n_seqs == 0) return 0;
+    const int rows = mdma_talking_attention_tile_rows(n_heads, n_kv_heads, dim, v_dim, max_new);
+    MDMA_REQUIRE(rows > 0, "talking_attention: the tiled kernel's shared memory does not fit %d heads of %d/%d", n_heads, dim, v_dim);
+    MDMA_REQUIRE(n_seqs <= 65535, "talking_attention: too many sequences");
+    const size_t smem = talk_tiled_smem(rows, n_heads, dim, v_dim);
+    dim3 grid((max_new + rows - 1) / rows, n_seqs);
+    MDMA_DISPATCH_DTYPE(dtype, T, {
+        static bool raised = false;
+        if (!raised) {
+            cudaFuncSetAttribute(talking_attention_tiled_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            raised = true;
+        }
+        launch_chained(talking_attention_tiled_kernel<T>, grid, dim3(kTalkWarps * 32), smem, stream, (const T*)q, q_row_stride,
+                       (const T*)k_cache, (const T*)v_cache, talk, sinks, seq_start, seq_pos0, seq_slot, page_table, max_pages,
+                       page_size, (T*)out, n_heads, n_kv_heads, dim, v_dim, window, scale, rows);
+    });
+    MDMA_LAUNCH_OK("talking_attention_tiled");
     return 0;
 }
 

@@ -797,18 +797,31 @@ def qk_norm_rotate(proj, k_col: int, v_col: int, tok_seq, tok_pos, seq_slot, inv
           _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(rotary_dim), _i(int(interleaved)), _i(int(write_kv)), _stream())
 
 
-def talking_attention(q, k_cache, v_cache, talk, sinks, tok_seq, tok_pos, seq_slot, page_table, max_pages: int,
-                      page_size: int, out, n_tokens: int, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int,
-                      scale: float) -> None:
+def talking_attention_tiled_fits(n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> bool:
+    """Whether the tiled kernel's shared memory takes this geometry at all (with tiles of one row at least)."""
+    lib = _build._loaded.get("core") or _build.load("core")
+    return n_heads % n_kv_heads == 0 and bool(lib.mdma_talking_attention_tile_rows(_i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(1)))
+
+
+def talking_attention(q, k_cache, v_cache, talk, sinks, ctx, page_table, max_pages: int, page_size: int, out,
+                      n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int, scale: float,
+                      tiled: bool = False) -> None:
     """out[t, h] = sum_j p_hj v_j with p_h the softmax over the keys up to the token's position of the MIXED scores
     sum_g talk[h, g] (q_g . k_j) scale; `sinks` [heads] float join each denominator as exp(sink_h); `talk` None: heads
-    on their own."""
-    _need_cuda(q, k_cache, v_cache, talk, sinks, tok_seq, tok_pos, seq_slot, page_table, out)
+    on their own.  `tiled`: the kernel that stages keys and values per tile of query rows (else a block per token
+    that visits the keys in position order)."""
+    _need_cuda(q, k_cache, v_cache, talk, sinks, page_table, out)
     assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == k_cache.dtype == v_cache.dtype
-    assert k_cache.is_contiguous() and v_cache.is_contiguous() and out.shape[1] == n_heads * v_dim
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and out.shape[1] == n_heads * v_dim and out.shape[0] >= ctx.n_tokens
     assert talk is None or (talk.dtype == torch.float32 and talk.is_contiguous() and talk.numel() == n_heads * n_heads)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads)
+    if tiled:
+        _call("core", "mdma_talking_attention_tiled", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(k_cache),
+              _ptr(v_cache), _ptr(talk), _ptr(sinks), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot),
+              _ptr(page_table), _i(max_pages), _i(page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs), _i(ctx.max_new),
+              _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _stream())
+        return
     _call("core", "mdma_talking_attention", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)), _ptr(k_cache), _ptr(v_cache),
-          _ptr(talk), _ptr(sinks), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), _i(max_pages),
-          _i(page_size), _ptr(out), _i(n_tokens), _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale),
+          _ptr(talk), _ptr(sinks), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_slot), _ptr(page_table), _i(max_pages),
+          _i(page_size), _ptr(out), _i(ctx.n_tokens), _i(n_heads), _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale),
           _stream())

@@ -126,6 +126,7 @@ class TalkingAttention(Part):
         if self.extra > 0:
             self.sinks = take((self.n_heads,), torch.float32)
             self.sinks.fill_(math.log(self.extra))
+        self._tiled_ok = ops.talking_attention_tiled_fits(self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim)
 
     def forward(self, ctx, h, x, view, owns_cache=True):
         n = ctx.n_tokens
@@ -141,9 +142,11 @@ class TalkingAttention(Part):
                            self.q_weight, self.k_weight, self.qk_norm, self.eps, view.k, view.v, view.page_table,
                            view.max_pages, view.page_size, n, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim,
                            rotary_dim, interleaved, owns_cache)
-        ops.talking_attention(row, view.k, view.v, self.talk_f32, self.sinks, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
-                              view.page_table, view.max_pages, view.page_size, out, n, self.n_heads, self.n_kv_heads,
-                              self.head_dim, self.v_dim, self.window, self.scale)
+        # the 32-bit engine visits keys in position order, a block per token; the serving engine stages tiles
+        tiled = self._tiled_ok and row.dtype != torch.float32
+        ops.talking_attention(row, view.k, view.v, self.talk_f32, self.sinks, ctx, view.page_table, view.max_pages,
+                              view.page_size, out, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, self.window,
+                              self.scale, tiled=tiled)
         self.o.accumulate(out, x, n)
 
     def resident_tensors(self):
