@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
     python bench.py --shape llama-2-7b | llama-3.2-1b [--batch B] [--prompt-len P] [--prefill-tokens T]
-    python bench.py --compare gevonex|mogevik|tubusun [--compare-widths 1024,2048,4096] [--compare-layers 4]
+    python bench.py --compare gevonex|mogevik|tubusun|fizadra [--compare-widths 1024,2048,4096] [--compare-layers 4]
 
 Prints ONE JSON line.  The default run has the layer sizes of the
 Llama-3.1-8B shape with random bfloat16 weights, a batch of 8 sequences
@@ -30,6 +30,11 @@ number of matrix elements a token uses.
 attention with a sink and head gates side by side with linear attention,
 norms around every sublayer, dense and routed feed-forwards) beside a Mogevik
 and a Llama of the same width, depth and vocabulary.
+
+`--compare fizadra` does the same for the Fizadra architecture (attention
+over a cached latent with a turned key part, attention whose heads' scores
+are mixed, grouped norms around every sublayer, a weighted sum over the
+depth) beside a Gevonex (the other model with a cached latent) and a Llama.
 """
 from __future__ import annotations
 
@@ -192,6 +197,30 @@ def tubusun_config(width: int, layers: int, vocab: int) -> dict:
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if i % 2 else moe} for i in range(layers)]}
 
 
+def fizadra_config(width: int, layers: int, vocab: int) -> dict:
+    """A Fizadra of `layers` layers (latent attention with a sink, attention with mixed scores, latent attention that
+    reads the first layer's cache, latent attention of the second form, ...) whose sizes follow the width: heads of
+    96 + 32 numbers over a latent of 96 with a turned part of 32 (cached vectors of 128, the widest the tensor-core
+    attention kernels take), a query latent of width / 4; query heads of 128 in groups of four with half a head
+    turned; a feed-forward of 4 x width; rows normed in four parts."""
+    heads = max(1, width // 128)
+    rot = {"base": 10000.0, "dims": 32}
+    scaled = dict(rot, scaling={"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+    latent = {"heads": heads, "dim": 96, "rot_dim": 32, "vdim": 128, "kv_rank": 96, "q_rank": max(64, width // 4 // 64 * 64),
+              "scale": 128 ** -0.5}
+    kinds = ["latent_attention", "attention", "latent_attention", "latent_attention_2"]
+    mixers = [dict(latent, rot=scaled), {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                         "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 64}},
+              dict(latent, rot=scaled, kv_from=0), dict(latent, rot=rot)]
+    out = []
+    for i in range(layers):
+        m = dict(mixers[i % 4])
+        if "kv_from" in m:
+            m["kv_from"] = i - 2
+        out.append({"type": kinds[i % 4], "mixer": m, "mlp": {"kind": "dense", "ff": 4 * width}})
+    return {"architecture": "Fizadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 4}, "layers": out}
+
+
 def expert_share(cfg: dict, name: str, draws: int) -> float:
     """The share of an expert's matrix that a step of `draws` tokens reads (decode: distinct experts among the
     draws, chosen evenly) or, with draws = 0, the share of tokens that use it (prefill)."""
@@ -297,6 +326,8 @@ def compare(args) -> int:
     rows = []
     for width in [int(w) for w in args.compare_widths.split(",")]:
         row = {"width": width, "layers": args.compare_layers, "vocab": vocab, "batch": args.batch}
+        if args.compare == "fizadra":
+            row["fizadra"] = measure(fizadra_config(width, args.compare_layers, vocab), args.batch)
         if args.compare == "tubusun":
             row["tubusun"] = measure(tubusun_config(width, args.compare_layers, vocab), args.batch)
         if args.compare in ("mogevik", "tubusun"):
@@ -305,7 +336,7 @@ def compare(args) -> int:
             row["gevonex"] = measure(gevonex_config(width, args.compare_layers, vocab), args.batch)
         row["llama"] = measure(llama_like(width, args.compare_layers, vocab), args.batch)
         rows.append(row)
-    beside = {"tubusun": "tubusun beside mogevik and llama", "mogevik": "mogevik beside gevonex and llama",
+    beside = {"fizadra": "fizadra beside gevonex and llama", "tubusun": "tubusun beside mogevik and llama", "mogevik": "mogevik beside gevonex and llama",
               "gevonex": "gevonex beside llama"}[args.compare]
     print(json.dumps({"compare": beside + " at equal width, depth and vocabulary", "dtype": args.dtype,
                       "prefill_tokens": T, "decode_after_prompts_of": prompt, "peaks": peak_src,
@@ -334,7 +365,7 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the true 32-bit engine (CUDA-core kernels), for the record; the headline is bfloat16")
-    ap.add_argument("--compare", default=None, choices=["gevonex", "mogevik", "tubusun"],
+    ap.add_argument("--compare", default=None, choices=["gevonex", "mogevik", "tubusun", "fizadra"],
                     help="another program: the named architecture beside a Llama of equal size (see the header)")
     ap.add_argument("--compare-widths", default="1024,2048,4096")
     ap.add_argument("--compare-layers", type=int, default=4)

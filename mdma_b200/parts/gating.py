@@ -165,7 +165,7 @@ class DepthAverage(Part):
             raise ValueError(f"a depth average of {self.terms} terms in a schedule of {self.depth} runs")
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.terms,), "vector", "normal")}
+        return {"weight": TensorSpec((self.terms,), "vector", "ones")}
 
     def workspace(self):
         return {f"depth_history_{self.depth}": (self.depth * self.width, "f32")}
