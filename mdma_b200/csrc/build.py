@@ -29,7 +29,7 @@ LIBRARIES = {
     "core": (["elementwise.cu", "gemm_simt.cu", "attention_simple.cu", "sampling.cu", "sequence_mix.cu",
              "latent_attention.cu", "rglru.cu", "attention_distance.cu", "routed_ffn.cu", "attention_prepare.cu",
              "linear_attention.cu", "group_norm.cu", "rotary_latent.cu", "attention_talking.cu"], ["common.cuh"], []),
-    "tensor": (["gemm_tcgen05.cu", "attention_mma.cu", "attention_tc.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh"], []),
+    "tensor": (["gemm_tcgen05.cu", "attention_mma.cu", "attention_tc.cu", "attention_talking_mma.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh"], []),
     "noalloc": (["attention_noalloc.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh", "attention_noalloc.h"], []),
 }
 

@@ -404,3 +404,40 @@ def wait_probe(mode: int, flag: torch.Tensor, st: Optional[TensorState] = None) 
     with the product kernels' own wait routines; a wait that runs out sets the status word."""
     st = st or _device_state(flag.device)
     _call("tensor", "mdma_wait_probe", _i(mode), _ptr(flag), _ptr(st.status), _stream())
+
+
+# ---- attention with mixed scores on the tensor cores (csrc/attention_talking_mma.cu) -----------------------------------
+def talking_attention_mma_warps(n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> int:
+    """Heads a block of the tensor-core kernel takes at a time for this geometry, or 0 if it does not take it (the
+    same arithmetic as the library's; kept here so that a memory plan needs no compiled library)."""
+    if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
+        return 0
+    kd = n_kv_heads * dim
+    if dim % 8 or kd % 16 or v_dim % 16 or not 0 < v_dim <= 128:
+        return 0
+    for w in (4, 2, 1):
+        if (w * 16 * (kd + 8) + 32 * (kd + 8) + w * 32 * (v_dim + 8)) * 2 <= 200 * 1024:
+            return w
+    return 0
+
+
+def talking_attention_mma(ctx, q: torch.Tensor, talk: torch.Tensor, x: torch.Tensor, view, sinks_log2: Optional[torch.Tensor],
+                          out: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int, scale: float,
+                          st: Optional[TensorState] = None) -> None:
+    """Attention whose heads' scores are mixed by `talk` [heads, heads] (float) before the softmax, bfloat16, on the
+    tensor cores.  `q`: rows whose first heads * dim columns are the queries; `x` [tokens, heads * kv_heads * dim]:
+    scratch for the mixed queries; `sinks_log2`: the sinks times log2(e), or None."""
+    _need_cuda(q, talk, x, view.k, view.v, sinks_log2, out, view.page_table)
+    if q.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention takes bfloat16")
+    kd = n_kv_heads * dim
+    assert q.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * v_dim and out.shape[0] >= ctx.n_tokens
+    assert x.is_contiguous() and x.shape[1] == n_heads * kd and x.shape[0] >= ctx.n_tokens
+    assert view.k.is_contiguous() and view.v.is_contiguous() and view.k.shape[-1] == dim and view.v.shape[-1] == v_dim
+    assert talk.dtype == torch.float32 and talk.is_contiguous() and talk.numel() == n_heads * n_heads
+    assert sinks_log2 is None or (sinks_log2.dtype == torch.float32 and sinks_log2.is_contiguous() and sinks_log2.numel() == n_heads)
+    flush_pending(q.device, st or _device_state(q.device))
+    _call("tensor", "mdma_talking_attention_mma", _ptr(q), _i(q.stride(0)), _ptr(talk), _ptr(x), _ptr(view.k), _ptr(view.v),
+          _ptr(sinks_log2), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
+          _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads),
+          _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _stream(), launches=2)

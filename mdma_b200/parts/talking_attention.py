@@ -9,7 +9,10 @@ query heads are mixed by a learned matrix T [heads, heads], s'_h = sum_g T[h, g]
 s'_h.  `denominator_extra` c > 0 adds c to every softmax denominator (a key with score ln c and no value; 1 is a sink
 whose score is 0).  The heads' results, concatenated, times Wo^T are added to the residual stream.
 
-Scores, mixing and softmax are float in both engines.
+Scores, mixing and softmax are float in both engines.  Where the serving engine's tensor-core kernel takes the sizes,
+the mixing is moved onto the queries: heads of one group share their key head, so s'_h = sum_c x_h,c . k_c with
+x_h,c = scale * sum_{g in group c} T[h, g] q_g, one dot product of kv_heads * dim numbers against the token's key heads
+side by side as the cache row holds them (x is formed in float and rounded once to bfloat16, the product sums in float).
 """
 from __future__ import annotations
 
@@ -55,6 +58,10 @@ class TalkingAttention(Part):
         self.k_col, self.v_col = self.q_width, self.q_width + self.k_width
         self.row_width = self.v_col + self.v_width
         self.row_pitch = -(-self.row_width // 8) * 8
+        # the tensor-core kernel works on queries mixed per kv group, side by side: kv_heads * dim numbers a head
+        from ..ops_tensor import talking_attention_mma_warps
+        self.mixed_width = self.n_heads * self.n_kv_heads * self.head_dim
+        self._mma_shape = self.talk and talking_attention_mma_warps(self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim) > 0
 
     def children(self):
         return [self.position] if self.position is not None else []
@@ -91,6 +98,7 @@ class TalkingAttention(Part):
             out["talk_f32"] = ((self.n_heads, self.n_heads), torch.float32)
         if self.extra > 0:
             out["sinks"] = ((self.n_heads,), torch.float32)
+            out["sinks_log2"] = ((self.n_heads,), torch.float32)
         return out
 
     def kv_need(self):
@@ -100,7 +108,10 @@ class TalkingAttention(Part):
         return None
 
     def workspace(self):
-        return {f"tqkv_{self.row_pitch}": (self.row_pitch, "act"), f"tattn_{self.out_width}": (self.out_width, "act")}
+        out = {f"tqkv_{self.row_pitch}": (self.row_pitch, "act"), f"tattn_{self.out_width}": (self.out_width, "act")}
+        if self._mma_shape:
+            out[f"tmixed_{self.mixed_width}"] = (self.mixed_width, "act")
+        return out
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
@@ -119,13 +130,15 @@ class TalkingAttention(Part):
         self.q_weight, self.k_weight = tensors.get("q.norm"), tensors.get("k.norm")
         self.talk_values = tensors.get("talk")
         take = rt.alloc if rt.alloc is not None else (lambda shape, dt: torch.zeros(shape, dtype=dt, device=fused.device))
-        self.talk_f32 = self.sinks = None
+        self.talk_f32 = self.sinks = self.sinks_log2 = None
         if self.talk:
             self.talk_f32 = take((self.n_heads, self.n_heads), torch.float32)      # the mixing is done in float
             self.talk_f32.copy_(self.talk_values.float())
         if self.extra > 0:
             self.sinks = take((self.n_heads,), torch.float32)
             self.sinks.fill_(math.log(self.extra))
+            self.sinks_log2 = take((self.n_heads,), torch.float32)      # the tensor-core kernel works in powers of two
+            self.sinks_log2.fill_(math.log2(self.extra))
         self._tiled_ok = ops.talking_attention_tiled_fits(self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim)
 
     def forward(self, ctx, h, x, view, owns_cache=True):
@@ -142,6 +155,13 @@ class TalkingAttention(Part):
                            self.q_weight, self.k_weight, self.qk_norm, self.eps, view.k, view.v, view.page_table,
                            view.max_pages, view.page_size, n, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim,
                            rotary_dim, interleaved, owns_cache)
+        if self._mma_shape and self.rt.attention == "fast" and row.dtype == torch.bfloat16:
+            from .. import ops_tensor
+            mixed = ctx.buf(f"tmixed_{self.mixed_width}", self.mixed_width)
+            ops_tensor.talking_attention_mma(ctx, row, self.talk_f32, mixed, view, self.sinks_log2, out, self.n_heads,
+                                             self.n_kv_heads, self.head_dim, self.v_dim, self.window, self.scale, st=self.rt.tc)
+            self.o.accumulate(out, x, n)
+            return
         # the 32-bit engine visits keys in position order, a block per token; the serving engine stages tiles
         tiled = self._tiled_ok and row.dtype != torch.float32
         ops.talking_attention(row, view.k, view.v, self.talk_f32, self.sinks, ctx, view.page_table, view.max_pages,

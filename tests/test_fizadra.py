@@ -356,8 +356,8 @@ def _plain_mixed_attention(q, k, v, talk, sink, scale, pos0):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tiled", [False, True])
-@pytest.mark.parametrize("H,G,D,V,talk,sink", [(6, 2, 24, 40, True, True), (5, 1, 12, 4, True, True), (4, 4, 96, 96, True, True),
+@pytest.mark.parametrize("tiled", [False, True, "mma"])
+@pytest.mark.parametrize("H,G,D,V,talk,sink", [(6, 2, 24, 40, True, True), (6, 2, 24, 48, True, True), (7, 1, 16, 16, True, False), (5, 1, 12, 4, True, True), (4, 4, 96, 96, True, True),
                                                (8, 2, 64, 64, True, False), (3, 3, 16, 16, False, True), (16, 4, 128, 128, True, True),
                                                (32, 8, 32, 48, True, True)])
 def test_attention_with_mixed_scores_far_key_pages_and_batches(dtype, tiled, H, G, D, V, talk, sink):
@@ -366,7 +366,12 @@ def test_attention_with_mixed_scores_far_key_pages_and_batches(dtype, tiled, H, 
     out for one head through one coordinate, so that a kernel that loses far keys, mixes the wrong heads or reads the
     wrong page shows.  Pages are scattered; every row nobody owns holds NaN."""
     from mdma_b200 import ops
-    if tiled and not ops.talking_attention_tiled_fits(H, G, D, V):
+    if tiled == "mma":
+        from mdma_b200 import ops_tensor
+        from mdma_b200.cache import KVView
+        if dtype != torch.bfloat16 or not talk or not ops_tensor.talking_attention_mma_warps(H, G, D, V):
+            pytest.skip("the tensor-core kernel takes bfloat16, a mixing matrix and sizes in sixteens")
+    elif tiled and not ops.talking_attention_tiled_fits(H, G, D, V):
         pytest.skip("beyond the tiled kernel's shared memory")
     g = torch.Generator().manual_seed(H * 13 + D + V)
     page, max_pages = 16, 24
@@ -399,7 +404,16 @@ def test_attention_with_mixed_scores_far_key_pages_and_batches(dtype, tiled, H, 
     qd = _dev(torch.cat([q.reshape(q.shape[0], -1) for q in qs]), dtype)
     out = torch.zeros(n, H * V, device="cuda", dtype=dtype)
     Td, Sd = (None if T is None else _dev(T)), (None if S is None else _dev(S))
-    ops.talking_attention(qd, kc, vc, Td, Sd, st, table.cuda(), max_pages, page, out, H, G, D, V, 0, scale, tiled=tiled)
+
+    def attend(q_rows, step, o):
+        if tiled == "mma":
+            x = torch.full((step.n_tokens + 1, H * G * D), float("nan"), device="cuda", dtype=dtype)
+            ops_tensor.talking_attention_mma(step, q_rows, Td, x, KVView(kc, vc, table.cuda(), page, max_pages, 0),
+                                             None if S is None else _dev(S * 1.4426950408889634), o, H, G, D, V, 0, scale)
+        else:
+            ops.talking_attention(q_rows, kc, vc, Td, Sd, step, table.cuda(), max_pages, page, o, H, G, D, V, 0, scale, tiled=tiled)
+
+    attend(qd, st, out)
     rd = lambda t: _dev(t, dtype).double().cpu()
     want = torch.cat([_plain_mixed_attention(rd(qs[s]), rd(ks[s]), rd(vs[s]), None if T is None else T.double(), S, scale, pos0[s])
                       .reshape(new[s], -1) for s in range(3)])
@@ -416,7 +430,7 @@ def test_attention_with_mixed_scores_far_key_pages_and_batches(dtype, tiled, H, 
     for s, slot in enumerate([3, 0, 5]):
         one = _Step([new[s]], [pos0[s]], [slot])
         alone = torch.zeros(new[s], H * V, device="cuda", dtype=dtype)
-        ops.talking_attention(qd[o:o + new[s]], kc, vc, Td, Sd, one, table.cuda(), max_pages, page, alone, H, G, D, V, 0, scale, tiled=tiled)
+        attend(qd[o:o + new[s]], one, alone)
         if dtype == torch.float32 and not tiled:
             assert torch.equal(alone, out[o:o + new[s]])
         else:
