@@ -9,8 +9,9 @@
 //
 // talking_mix:        x[t, h, :] from q[t, :, :] and T, times scale * log2(e), rounded once to bfloat16.
 // talking_attention_mma: block = 16 query rows of one sequence x up to four heads (a warp each).  Keys are walked 32
-//   at a time: the key rows of the chunk (all kv heads, one contiguous vector per key) are staged in shared memory
-//   once for the block's heads, each warp stages the values of its own kv head.  S = X K^T by mma.sync with X and K
+//   at a time: the key rows of the chunk (all kv heads, one contiguous vector per key) are copied into shared memory
+//   once for the block's heads (cp.async; with 108 KB a block two blocks share an SM, so one multiplies while the
+//   other waits for its copies); the value rows once for the block when its heads are of one group, else per warp.  S = X K^T by mma.sync with X and K
 //   fragments by ldmatrix; mask; online softmax in float with base-2 exponentials; P rounded to bfloat16 in registers
 //   is the A operand of O += P V, V fragments by transposed ldmatrix.  Rows of the chunk that no key owns are
 //   zero-filled, never loaded.  The denominator takes 2^sink_h at the end when sinks are given.
@@ -32,6 +33,11 @@ __device__ __forceinline__ void tm_mma(float* c, uint32_t a0, uint32_t a1, uint3
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void tm_copy16(void* dst_shared, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void tm_copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tm_copies_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ uint32_t tm_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -47,7 +53,7 @@ talking_mix_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
     const int group = n_heads / n_kv_heads, kd = n_kv_heads * dim;
     const __nv_bfloat16* qr = q + t * q_row_stride;
     for (int e = threadIdx.x; e < n_heads * kd; e += blockDim.x) {
-        const int h = e / kd, c = (e % kd) / dim, d = e % dim;
+        const int h = e / kd, cd = e - h * kd, c = cd / dim, d = cd - c * dim;
         float acc = 0.f;
         for (int g = 0; g < group; ++g)
             acc = fmaf(talk[h * n_heads + c * group + g], __bfloat162float(qr[(size_t)(c * group + g) * dim + d]), acc);
@@ -55,9 +61,12 @@ talking_mix_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
     }
 }
 
-static size_t tm_smem_bytes(int warps, int kd, int v_dim) {
-    return ((size_t)warps * kTmRows * (kd + 8) + (size_t)kTmChunk * (kd + 8) + (size_t)warps * kTmChunk * (v_dim + 8)) * 2;
+// the block's mixed queries, a chunk's key rows, and its value rows: once when the block's heads are of one group
+// (`v_regions` 1), else once per warp
+static size_t tm_smem_bytes(int warps, int v_regions, int kd, int v_dim) {
+    return ((size_t)warps * kTmRows * (kd + 8) + (size_t)kTmChunk * (kd + 8) + (size_t)v_regions * kTmChunk * (v_dim + 8)) * 2;
 }
+constexpr size_t kTmSmemLimit = 220 * 1024;
 
 // VT: value n-tiles of eight columns (v_dim / 8) the accumulators are sized for.
 template <int VT>
@@ -84,7 +93,8 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
     const int kd = n_kv_heads * dim, qp = kd + 8, vp = v_dim + 8;         // row pitches in elements (16 bytes of padding)
     __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(tm_smem);         // [warps][16][kd + 8]
     __nv_bfloat16* sk = sx + (size_t)warps * kTmRows * qp;                 // [32][kd + 8]
-    __nv_bfloat16* sv = sk + (size_t)kTmChunk * qp + (size_t)warp * kTmChunk * vp;   // this warp's [32][v_dim + 8]
+    const bool shared_v = group % warps == 0;                              // the block's heads read one kv head
+    __nv_bfloat16* sv = sk + (size_t)kTmChunk * qp + (shared_v ? 0 : (size_t)warp * kTmChunk * vp);   // [32][v_dim + 8]
     __nv_bfloat16* sxw = sx + (size_t)warp * kTmRows * qp;
     const int pos0 = seq_pos0[s] + r0, last = pos0 + rows - 1;
     const int first = window > 0 ? max(0, pos0 + 1 - window) : 0;
@@ -103,38 +113,47 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
     for (int n = 0; n < VT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;       // rows lane/4 and lane/4 + 8
     const int row_lo = lane >> 2, row_hi = row_lo + 8;
-    const uint32_t sx_addr = (uint32_t)__cvta_generic_to_shared(sxw), sk_addr = (uint32_t)__cvta_generic_to_shared(sk),
-                   sv_addr = (uint32_t)__cvta_generic_to_shared(sv);
+    const uint32_t sx_addr = (uint32_t)__cvta_generic_to_shared(sxw);
 
+    // a chunk's key rows and value rows, asked for 16 bytes at a time (a warp takes whole rows: one look at the page
+    // table per row); rows no key owns: zero.  Two blocks share an SM: while one waits for its copies the other multiplies.
+    const int k_cols = kd / 8, v_cols = v_dim / 8;
     for (int c0 = first; c0 <= last; c0 += kTmChunk) {
         const int n_keys = min(kTmChunk, last + 1 - c0);
         __syncthreads();                                   // every warp is done with the chunk before
-        for (int e = threadIdx.x; e < kTmChunk * (kd / 8); e += blockDim.x) {
-            const int j = e / (kd / 8), d8 = e % (kd / 8);
-            uint4 v = zero4;
+        for (int j = warp; j < kTmChunk; j += warps) {
+            __nv_bfloat16* dst = sk + (size_t)j * qp;
             if (j < n_keys) {
                 const int p = c0 + j;
-                v = *reinterpret_cast<const uint4*>(k_cache + ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * kd + d8 * 8);
+                const __nv_bfloat16* src = k_cache + ((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * kd;
+                for (int d8 = lane; d8 < k_cols; d8 += 32) tm_copy16(dst + d8 * 8, src + d8 * 8);
+            } else {
+                for (int d8 = lane; d8 < k_cols; d8 += 32) *reinterpret_cast<uint4*>(dst + d8 * 8) = zero4;
             }
-            *reinterpret_cast<uint4*>(sk + (size_t)j * qp + d8 * 8) = v;
         }
         if (active) {
-            for (int e = lane; e < kTmChunk * (v_dim / 8); e += 32) {
-                const int j = e / (v_dim / 8), d8 = e % (v_dim / 8);
-                uint4 v = zero4;
+            // value rows: the block's warps share the work when they share the kv head, else every warp its own
+            for (int j = shared_v ? warp : 0; j < kTmChunk; j += shared_v ? warps : 1) {
+                __nv_bfloat16* dst = sv + (size_t)j * vp;
                 if (j < n_keys) {
                     const int p = c0 + j;
-                    v = *reinterpret_cast<const uint4*>(v_cache + (((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh) * v_dim + d8 * 8);
+                    const __nv_bfloat16* src = v_cache + (((size_t)pages[p / page_size] * page_size + (size_t)(p % page_size)) * n_kv_heads + kvh) * v_dim;
+                    for (int d8 = lane; d8 < v_cols; d8 += 32) tm_copy16(dst + d8 * 8, src + d8 * 8);
+                } else {
+                    for (int d8 = lane; d8 < v_cols; d8 += 32) *reinterpret_cast<uint4*>(dst + d8 * 8) = zero4;
                 }
-                *reinterpret_cast<uint4*>(sv + (size_t)j * vp + d8 * 8) = v;
             }
         }
+        tm_copies_commit();
+        tm_copies_wait();
         __syncthreads();
         if (!active) continue;
+        const uint32_t sk_addr = (uint32_t)__cvta_generic_to_shared(sk), sv_addr = (uint32_t)__cvta_generic_to_shared(sv);
         // S [16 x 32] = X [16 x kd] K^T
         float sc[4][4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+#pragma unroll 4
         for (int k0 = 0; k0 < kd; k0 += 16) {
             uint32_t a0, a1, a2, a3;
             tm_ldmatrix_x4(sx_addr + (uint32_t)(((lane & 15) * qp + k0 + (lane >> 4) * 8) * 2), a0, a1, a2, a3);
@@ -233,8 +252,9 @@ static int tm_warps_for(int n_heads, int n_kv_heads, int dim, int v_dim) {
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
     const int kd = n_kv_heads * dim;
     if (dim % 8 || kd % 16 || v_dim % 16 || v_dim > kTmMaxV || v_dim <= 0) return 0;
-    for (int w = kTmMaxWarps; w >= 1; w >>= 1)
-        if (tm_smem_bytes(w, kd, v_dim) <= 200 * 1024) return w;
+    const int group = n_heads / n_kv_heads;
+    for (int w = kTmMaxWarps; w >= 2; w >>= 1)          // one head a block would leave the tensor cores waiting
+        if (tm_smem_bytes(w, group % w == 0 ? 1 : w, kd, v_dim) <= kTmSmemLimit) return w;
     return 0;
 }
 
@@ -265,13 +285,13 @@ int mdma_talking_attention_mma(const void* q, int q_row_stride, const float* tal
     launch_chained(talking_mix_kernel, dim3(n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)q, q_row_stride, talk,
                    (__nv_bfloat16*)x, n_heads, n_kv_heads, dim, scale * 1.4426950408889634f);
     MDMA_LAUNCH_OK("talking_mix");
-    const size_t smem = tm_smem_bytes(warps, n_kv_heads * dim, v_dim);
+    const size_t smem = tm_smem_bytes(warps, (n_heads / n_kv_heads) % warps == 0 ? 1 : warps, n_kv_heads * dim, v_dim);
     dim3 grid((max_new + kTmRows - 1) / kTmRows, (n_heads + warps - 1) / warps, n_seqs);
 #define MDMA_TM_LAUNCH(VT)                                                                                                  \
     do {                                                                                                                    \
         static bool raised = false;                                                                                         \
         if (!raised) {                                                                                                      \
-            cudaFuncSetAttribute(talking_attention_mma_kernel<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            cudaFuncSetAttribute(talking_attention_mma_kernel<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTmSmemLimit); \
             raised = true;                                                                                                  \
         }                                                                                                                   \
         launch_chained(talking_attention_mma_kernel<VT>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,    \

@@ -415,8 +415,9 @@ def talking_attention_mma_warps(n_heads: int, n_kv_heads: int, dim: int, v_dim: 
     kd = n_kv_heads * dim
     if dim % 8 or kd % 16 or v_dim % 16 or not 0 < v_dim <= 128:
         return 0
-    for w in (4, 2, 1):
-        if (w * 16 * (kd + 8) + 32 * (kd + 8) + w * 32 * (v_dim + 8)) * 2 <= 200 * 1024:
+    group = n_heads // n_kv_heads
+    for w in (4, 2):
+        if (w * 16 * (kd + 8) + 32 * (kd + 8) + (1 if group % w == 0 else w) * 32 * (v_dim + 8)) * 2 <= 220 * 1024:
             return w
     return 0
 
