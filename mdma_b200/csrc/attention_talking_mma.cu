@@ -14,7 +14,8 @@
 //   other waits for its copies); the value rows once for the block when its heads are of one group, else per warp.  S = X K^T by mma.sync with X and K
 //   fragments by ldmatrix; mask; online softmax in float with base-2 exponentials; P rounded to bfloat16 in registers
 //   is the A operand of O += P V, V fragments by transposed ldmatrix.  Rows of the chunk that no key owns are
-//   zero-filled, never loaded.  The denominator takes 2^sink_h at the end when sinks are given.
+//   zero-filled, never loaded.  The denominator takes 2^sink_h at the end when sinks are given.  Single tokens of
+//   a few sequences: the keys are divided over `splits` blocks that leave unnormalised sums, merged in split order.
 #include "common.cuh"
 
 namespace mdma {
@@ -50,14 +51,17 @@ talking_mix_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
     chain_release();
     chain_wait();
     const size_t t = blockIdx.x;
+    const int h = blockIdx.y;                              // a block per (token, head)
     const int group = n_heads / n_kv_heads, kd = n_kv_heads * dim;
     const __nv_bfloat16* qr = q + t * q_row_stride;
-    for (int e = threadIdx.x; e < n_heads * kd; e += blockDim.x) {
-        const int h = e / kd, cd = e - h * kd, c = cd / dim, d = cd - c * dim;
+    for (int e = threadIdx.x; e < kd; e += blockDim.x) {
+        const int c = e / dim, d = e - c * dim;
+        const float* tw = talk + h * n_heads + c * group;
+        const __nv_bfloat16* qc = qr + (size_t)c * group * dim + d;
         float acc = 0.f;
-        for (int g = 0; g < group; ++g)
-            acc = fmaf(talk[h * n_heads + c * group + g], __bfloat162float(qr[(size_t)(c * group + g) * dim + d]), acc);
-        x[t * (size_t)n_heads * kd + e] = __float2bfloat16_rn(acc * factor);
+#pragma unroll 4
+        for (int g = 0; g < group; ++g) acc = fmaf(tw[g], __bfloat162float(qc[(size_t)g * dim]), acc);
+        x[(t * n_heads + h) * (size_t)kd + e] = __float2bfloat16_rn(acc * factor);
     }
 }
 
@@ -76,13 +80,14 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
                              const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                              const int* __restrict__ seq_slot, const int* __restrict__ page_table, int max_pages,
                              int page_size, __nv_bfloat16* __restrict__ out, int n_heads, int n_kv_heads, int dim, int v_dim,
-                             int window) {
+                             int window, int splits, float* __restrict__ partial) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(16) unsigned char tm_smem[];
     const int s = blockIdx.z;
     const int t0 = seq_start[s], n_new = seq_start[s + 1] - t0;
-    const int r0 = blockIdx.x * kTmRows;
+    const int split = blockIdx.x % splits;
+    const int r0 = (blockIdx.x / splits) * kTmRows;
     if (r0 >= n_new) return;
     const int rows = min(kTmRows, n_new - r0);
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,7 +123,11 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
     // a chunk's key rows and value rows, asked for 16 bytes at a time (a warp takes whole rows: one look at the page
     // table per row); rows no key owns: zero.  Two blocks share an SM: while one waits for its copies the other multiplies.
     const int k_cols = kd / 8, v_cols = v_dim / 8;
-    for (int c0 = first; c0 <= last; c0 += kTmChunk) {
+    // with `splits` > 1 this block takes a run of the tile's chunks and leaves unnormalised sums for the merge kernel
+    const int n_chunks = (last + 1 - first + kTmChunk - 1) / kTmChunk, per_split = (n_chunks + splits - 1) / splits;
+    const int c_begin = first + split * per_split * kTmChunk;
+    const int c_end = min(last, first + (split + 1) * per_split * kTmChunk - 1);
+    for (int c0 = c_begin; c0 <= c_end; c0 += kTmChunk) {
         const int n_keys = min(kTmChunk, last + 1 - c0);
         __syncthreads();                                   // every warp is done with the chunk before
         for (int j = warp; j < kTmChunk; j += warps) {
@@ -226,6 +235,34 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
         }
     }
     if (!active) return;
+    if (splits > 1) {
+        // [(token, head), split][v_dim + 2]: sums, running maximum, normaliser
+#pragma unroll
+        for (int n = 0; n < VT; ++n) {
+            const int d = n * 8 + (lane & 3) * 2;
+            if (d < v_dim) {
+                if (row_lo < rows) {
+                    float* dst = partial + (((size_t)(t0 + r0 + row_lo) * n_heads + h) * splits + split) * (v_dim + 2);
+                    dst[d] = o[n][0]; dst[d + 1] = o[n][1];
+                }
+                if (row_hi < rows) {
+                    float* dst = partial + (((size_t)(t0 + r0 + row_hi) * n_heads + h) * splits + split) * (v_dim + 2);
+                    dst[d] = o[n][2]; dst[d + 1] = o[n][3];
+                }
+            }
+        }
+        if ((lane & 3) == 0) {
+            if (row_lo < rows) {
+                float* dst = partial + (((size_t)(t0 + r0 + row_lo) * n_heads + h) * splits + split) * (v_dim + 2);
+                dst[v_dim] = m_lo; dst[v_dim + 1] = l_lo;
+            }
+            if (row_hi < rows) {
+                float* dst = partial + (((size_t)(t0 + r0 + row_hi) * n_heads + h) * splits + split) * (v_dim + 2);
+                dst[v_dim] = m_hi; dst[v_dim + 1] = l_hi;
+            }
+        }
+        return;
+    }
     if (sinks_log2 != nullptr) {
         const float sk2 = sinks_log2[h];
         const float a_lo = fmaxf(m_lo, sk2), a_hi = fmaxf(m_hi, sk2);
@@ -245,6 +282,33 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
             if (row_hi < rows)
                 *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + r0 + row_hi) * n_heads + h) * v_dim + d) = tm_pack(o[n][2] * i_hi, o[n][3] * i_hi);
         }
+    }
+}
+
+// out[t, h] = sum_s o_s 2^(m_s - M) / (sum_s l_s 2^(m_s - M) + 2^(sink_h - M)), splits in their order; a warp per (t, h)
+__global__ void __launch_bounds__(128)
+talking_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sinks_log2, __nv_bfloat16* __restrict__ out,
+                     int n_pairs, int n_heads, int v_dim, int splits) {
+    chain_release();
+    chain_wait();
+    const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (pair >= n_pairs) return;
+    const float* src = partial + (size_t)pair * splits * (v_dim + 2);
+    float M = sinks_log2 ? sinks_log2[pair % n_heads] : -INFINITY;
+    for (int k = 0; k < splits; ++k) M = fmaxf(M, src[(size_t)k * (v_dim + 2) + v_dim]);
+    float L = sinks_log2 ? exp2f(sinks_log2[pair % n_heads] - M) : 0.f;
+    for (int k = 0; k < splits; ++k) {
+        const float m = src[(size_t)k * (v_dim + 2) + v_dim];
+        if (m != -INFINITY) L += src[(size_t)k * (v_dim + 2) + v_dim + 1] * exp2f(m - M);
+    }
+    const float inv = 1.0f / L;
+    for (int d = lane; d < v_dim; d += 32) {
+        float acc = 0.f;
+        for (int k = 0; k < splits; ++k) {
+            const float m = src[(size_t)k * (v_dim + 2) + v_dim];
+            if (m != -INFINITY) acc = fmaf(src[(size_t)k * (v_dim + 2) + d], exp2f(m - M), acc);
+        }
+        out[(size_t)pair * v_dim + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -274,19 +338,20 @@ int mdma_talking_attention_mma(const void* q, int q_row_stride, const float* tal
                                const void* v_cache, const float* sinks_log2, const int* seq_start, const int* seq_pos0,
                                const int* seq_slot, const int* page_table, int max_pages, int page_size, void* out,
                                int n_tokens, int n_seqs, int max_new, int n_heads, int n_kv_heads, int dim, int v_dim,
-                               int window, float scale, cudaStream_t stream) {
+                               int window, float scale, int splits, float* partial, cudaStream_t stream) {
     const int warps = tm_warps_for(n_heads, n_kv_heads, dim, v_dim);
     MDMA_REQUIRE(warps > 0, "talking_attention_mma: %d/%d heads of %d/%d are not a geometry this kernel takes", n_heads, n_kv_heads, dim, v_dim);
     MDMA_REQUIRE(talk && x && page_table && page_size > 0 && max_pages > 0 && window >= 0 && seq_start && seq_pos0, "talking_attention_mma: bad arguments");
     MDMA_REQUIRE(n_seqs <= 65535 && (n_heads + warps - 1) / warps <= 65535, "talking_attention_mma: too many sequences or heads");
     MDMA_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)out & 3) == 0,
                  "talking_attention_mma: pointers must be 16-byte aligned");
+    MDMA_REQUIRE(splits >= 1 && (splits == 1 || partial), "talking_attention_mma: split keys need scratch");
     if (n_tokens == 0 || n_seqs == 0) return 0;
-    launch_chained(talking_mix_kernel, dim3(n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)q, q_row_stride, talk,
+    launch_chained(talking_mix_kernel, dim3(n_tokens, n_heads), dim3(256), 0, stream, (const __nv_bfloat16*)q, q_row_stride, talk,
                    (__nv_bfloat16*)x, n_heads, n_kv_heads, dim, scale * 1.4426950408889634f);
     MDMA_LAUNCH_OK("talking_mix");
     const size_t smem = tm_smem_bytes(warps, (n_heads / n_kv_heads) % warps == 0 ? 1 : warps, n_kv_heads * dim, v_dim);
-    dim3 grid((max_new + kTmRows - 1) / kTmRows, (n_heads + warps - 1) / warps, n_seqs);
+    dim3 grid(((max_new + kTmRows - 1) / kTmRows) * splits, (n_heads + warps - 1) / warps, n_seqs);
 #define MDMA_TM_LAUNCH(VT)                                                                                                  \
     do {                                                                                                                    \
         static bool raised = false;                                                                                         \
@@ -297,13 +362,18 @@ int mdma_talking_attention_mma(const void* q, int q_row_stride, const float* tal
         launch_chained(talking_attention_mma_kernel<VT>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,    \
                        (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, sinks_log2, seq_start, seq_pos0,      \
                        seq_slot, page_table, max_pages, page_size, (__nv_bfloat16*)out, n_heads, n_kv_heads, dim, v_dim,   \
-                       window);                                                                                             \
+                       window, splits, partial);                                                                            \
     } while (0)
     if (v_dim <= 32) MDMA_TM_LAUNCH(4);
     else if (v_dim <= 64) MDMA_TM_LAUNCH(8);
     else MDMA_TM_LAUNCH(16);
 #undef MDMA_TM_LAUNCH
     MDMA_LAUNCH_OK("talking_attention_mma");
+    if (splits > 1) {
+        launch_chained(talking_merge_kernel, dim3((n_tokens * n_heads + 3) / 4), dim3(128), 0, stream, (const float*)partial,
+                       sinks_log2, (__nv_bfloat16*)out, n_tokens * n_heads, n_heads, v_dim, splits);
+        MDMA_LAUNCH_OK("talking_merge");
+    }
     return 0;
 }
 

@@ -34,7 +34,34 @@ group_rmsnorm_kernel(const float* src, float* y_complete, const float* __restric
         const int g = g0 + warp / slices, s = warp % slices;
         const int lo = g * part + s * per_slice, hi = min(g * part + part, lo + per_slice);
         float sq = 0.f;
-        if (g < groups) {
+        // four numbers a lane at a time where the slice allows 16-byte accesses; a K-split product's partial sums are
+        // asked for four splits at a time (independent loads) and added in split order
+        const bool vec = (width & 3) == 0 && (lo & 3) == 0 && (hi & 3) == 0;
+        if (g < groups && vec) {
+            for (int e = lo + lane * 4; e < hi; e += 128) {
+                float4 v = *reinterpret_cast<const float4*>(xr + e);
+                if (ADD && splits > 0) {
+                    const float* pp = partial + r * width + e;
+                    int k = 0;
+                    for (; k + 4 <= splits; k += 4) {
+                        const float4 p0 = *reinterpret_cast<const float4*>(pp + (size_t)k * split_stride);
+                        const float4 p1 = *reinterpret_cast<const float4*>(pp + (size_t)(k + 1) * split_stride);
+                        const float4 p2 = *reinterpret_cast<const float4*>(pp + (size_t)(k + 2) * split_stride);
+                        const float4 p3 = *reinterpret_cast<const float4*>(pp + (size_t)(k + 3) * split_stride);
+                        v.x = (((v.x + p0.x) + p1.x) + p2.x) + p3.x;
+                        v.y = (((v.y + p0.y) + p1.y) + p2.y) + p3.y;
+                        v.z = (((v.z + p0.z) + p1.z) + p2.z) + p3.z;
+                        v.w = (((v.w + p0.w) + p1.w) + p2.w) + p3.w;
+                    }
+                    for (; k < splits; ++k) {
+                        const float4 p0 = *reinterpret_cast<const float4*>(pp + (size_t)k * split_stride);
+                        v.x += p0.x; v.y += p0.y; v.z += p0.z; v.w += p0.w;
+                    }
+                    *reinterpret_cast<float4*>(y_complete + r * width + e) = v;
+                }
+                sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
+            }
+        } else if (g < groups) {
             for (int e = lo + lane; e < hi; e += 32) {
                 float v = xr[e];
                 if (ADD) {
@@ -69,7 +96,38 @@ depth_mix_kernel(float* __restrict__ x, const float* __restrict__ x0, float* __r
     chain_wait();
     const size_t t = blockIdx.x;
     float* hist = history + t * (size_t)depth * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    if ((width & 3) == 0) {
+        // four numbers a thread; the earlier results are asked for four at a time, added in the order of j
+        const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+        if (e >= width) return;
+        const float4 mine = *reinterpret_cast<const float4*>(x + t * width + e);
+        *reinterpret_cast<float4*>(hist + (size_t)run * width + e) = mine;
+        const float4 first = *reinterpret_cast<const float4*>(x0 + t * width + e);
+        const float w0 = to_float(w[0]);
+        float4 acc = make_float4(w0 * first.x, w0 * first.y, w0 * first.z, w0 * first.w);
+        int j = 0;
+        for (; j + 4 <= run; j += 4) {
+            float4 h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = *reinterpret_cast<const float4*>(hist + (size_t)(j + i) * width + e);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float wj = to_float(w[j + i + 1]);
+                acc.x = fmaf(wj, h[i].x, acc.x); acc.y = fmaf(wj, h[i].y, acc.y);
+                acc.z = fmaf(wj, h[i].z, acc.z); acc.w = fmaf(wj, h[i].w, acc.w);
+            }
+        }
+        for (; j < run; ++j) {
+            const float4 h = *reinterpret_cast<const float4*>(hist + (size_t)j * width + e);
+            const float wj = to_float(w[j + 1]);
+            acc.x = fmaf(wj, h.x, acc.x); acc.y = fmaf(wj, h.y, acc.y); acc.z = fmaf(wj, h.z, acc.z); acc.w = fmaf(wj, h.w, acc.w);
+        }
+        const float wl = to_float(w[run + 1]);
+        acc.x = fmaf(wl, mine.x, acc.x); acc.y = fmaf(wl, mine.y, acc.y); acc.z = fmaf(wl, mine.z, acc.z); acc.w = fmaf(wl, mine.w, acc.w);
+        *reinterpret_cast<float4*>(x + t * width + e) = acc;
+        return;
+    }
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < width; e += gridDim.y * blockDim.x) {
         const float mine = x[t * width + e];
         hist[(size_t)run * width + e] = mine;
         float acc = to_float(w[0]) * x0[t * width + e];
@@ -116,6 +174,7 @@ int mdma_group_rmsnorm_add(float* x, float* y, const float* partial, int splits,
                            int w_dtype, int n_rows, int width, int groups, float eps, cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0 && groups > 0 && width % groups == 0, "group_rmsnorm_add: %d numbers do not split into %d parts", width, groups);
     MDMA_REQUIRE(splits >= 0 && (splits == 0 || partial), "group_rmsnorm_add: partial sums need a pointer");
+    MDMA_REQUIRE(splits == 0 || (((uintptr_t)partial & 15) == 0 && (split_stride & 3) == 0) || (width & 3) != 0, "group_rmsnorm_add: partial sums must be 16-byte aligned");
     if (n_rows == 0) return 0;
     int slices, warps;
     group_norm_shape(width, groups, &slices, &warps);
@@ -132,8 +191,8 @@ int mdma_depth_mix(float* x, const float* x0, float* history, int depth, int run
     MDMA_REQUIRE(n_rows >= 0 && width > 0 && depth > 0 && run >= 0 && run < depth, "depth_mix: run %d of %d", run, depth);
     if (n_rows == 0) return 0;
     MDMA_DISPATCH_DTYPE(w_dtype, TW,
-        launch_chained(depth_mix_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, x, x0, history, depth, run, (const TW*)w,
-                       width));
+        launch_chained(depth_mix_kernel<TW>, dim3(n_rows, (width & 3) == 0 ? (width / 4 + 255) / 256 : (width + 1023) / 1024),
+                       dim3(256), 0, stream, x, x0, history, depth, run, (const TW*)w, width));
     MDMA_LAUNCH_OK("depth_mix");
     return 0;
 }

@@ -424,10 +424,12 @@ def talking_attention_mma_warps(n_heads: int, n_kv_heads: int, dim: int, v_dim: 
 
 def talking_attention_mma(ctx, q: torch.Tensor, talk: torch.Tensor, x: torch.Tensor, view, sinks_log2: Optional[torch.Tensor],
                           out: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, window: int, scale: float,
-                          st: Optional[TensorState] = None) -> None:
+                          st: Optional[TensorState] = None, splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
     """Attention whose heads' scores are mixed by `talk` [heads, heads] (float) before the softmax, bfloat16, on the
     tensor cores.  `q`: rows whose first heads * dim columns are the queries; `x` [tokens, heads * kv_heads * dim]:
-    scratch for the mixed queries; `sinks_log2`: the sinks times log2(e), or None."""
+    scratch for the mixed queries; `sinks_log2`: the sinks times log2(e), or None.  `splits` > 1: the keys of every row
+    are divided over that many blocks, whose sums go through `partial` (tokens * heads * splits * (v_dim + 2) floats)
+    and are merged in split order."""
     _need_cuda(q, talk, x, view.k, view.v, sinks_log2, out, view.page_table)
     if q.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16")
@@ -437,8 +439,25 @@ def talking_attention_mma(ctx, q: torch.Tensor, talk: torch.Tensor, x: torch.Ten
     assert view.k.is_contiguous() and view.v.is_contiguous() and view.k.shape[-1] == dim and view.v.shape[-1] == v_dim
     assert talk.dtype == torch.float32 and talk.is_contiguous() and talk.numel() == n_heads * n_heads
     assert sinks_log2 is None or (sinks_log2.dtype == torch.float32 and sinks_log2.is_contiguous() and sinks_log2.numel() == n_heads)
+    if splits > 1:
+        _need_cuda(partial)
+        assert partial.dtype == torch.float32 and partial.is_contiguous()
+        assert partial.numel() >= ctx.n_tokens * n_heads * splits * (v_dim + 2)
     flush_pending(q.device, st or _device_state(q.device))
     _call("tensor", "mdma_talking_attention_mma", _ptr(q), _i(q.stride(0)), _ptr(talk), _ptr(x), _ptr(view.k), _ptr(view.v),
           _ptr(sinks_log2), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
           _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads),
-          _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _stream(), launches=2)
+          _i(n_kv_heads), _i(dim), _i(v_dim), _i(window), _f(scale), _i(splits), _ptr(partial if splits > 1 else None), _stream(),
+          launches=3 if splits > 1 else 2)
+
+
+def talking_attention_splits(most_seqs: int, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, sms: int) -> int:
+    """Into how many runs the keys of a single-token step are divided: as many as keep every block resident at once,
+    eight at most.  From the engine's capacity, not the live batch, so that a request's sums are added in the same order
+    whoever shares its step."""
+    warps = talking_attention_mma_warps(n_heads, n_kv_heads, dim, v_dim)
+    if not warps:
+        return 1
+    blocks = max(1, most_seqs) * -(-n_heads // warps)
+    return max(1, min(8, sms // blocks))
+

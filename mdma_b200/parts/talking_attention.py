@@ -158,8 +158,22 @@ class TalkingAttention(Part):
         if self._mma_shape and self.rt.attention == "fast" and row.dtype == torch.bfloat16:
             from .. import ops_tensor
             mixed = ctx.buf(f"tmixed_{self.mixed_width}", self.mixed_width)
+            splits, partial = 1, None
+            if ctx.max_new == 1:
+                # single tokens: the keys are divided over blocks.  The sums go through the rows of the mixed-query buffer
+                # that a step of single tokens cannot reach (it has a row per token of a pass, a step of single tokens
+                # uses a row per sequence); where those do not hold them, the keys stay whole.
+                most = int(getattr(ctx, "most_seqs", None) or ctx.n_seqs)
+                sms = self.rt.tc.sms if self.rt.tc is not None else 148
+                splits = ops_tensor.talking_attention_splits(most, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, sms)
+                spare = (mixed.shape[0] - most) * self.mixed_width // 2            # floats behind the rows in use
+                if splits > 1 and mixed.is_contiguous() and spare >= most * self.n_heads * splits * (self.v_dim + 2):
+                    partial = mixed.view(-1)[most * self.mixed_width:].view(torch.float32)
+                else:
+                    splits = 1
             ops_tensor.talking_attention_mma(ctx, row, self.talk_f32, mixed, view, self.sinks_log2, out, self.n_heads,
-                                             self.n_kv_heads, self.head_dim, self.v_dim, self.window, self.scale, st=self.rt.tc)
+                                             self.n_kv_heads, self.head_dim, self.v_dim, self.window, self.scale, st=self.rt.tc,
+                                             splits=splits, partial=partial)
             self.o.accumulate(out, x, n)
             return
         # the 32-bit engine visits keys in position order, a block per token; the serving engine stages tiles

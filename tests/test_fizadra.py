@@ -408,8 +408,12 @@ def test_attention_with_mixed_scores_far_key_pages_and_batches(dtype, tiled, H, 
     def attend(q_rows, step, o):
         if tiled == "mma":
             x = torch.full((step.n_tokens + 1, H * G * D), float("nan"), device="cuda", dtype=dtype)
+            parts = 5 if step.max_new == 1 else 1             # a single token: its keys divided over five blocks
+            scratch = torch.full((step.n_tokens * H * parts * (V + 2) + 3,), float("nan"), device="cuda")
             ops_tensor.talking_attention_mma(step, q_rows, Td, x, KVView(kc, vc, table.cuda(), page, max_pages, 0),
-                                             None if S is None else _dev(S * 1.4426950408889634), o, H, G, D, V, 0, scale)
+                                             None if S is None else _dev(S * 1.4426950408889634), o, H, G, D, V, 0, scale,
+                                             splits=parts, partial=scratch)
+            assert torch.isnan(scratch[-3:]).all() and torch.isnan(x[-1]).all()
         else:
             ops.talking_attention(q_rows, kc, vc, Td, Sd, step, table.cuda(), max_pages, page, o, H, G, D, V, 0, scale, tiled=tiled)
 
