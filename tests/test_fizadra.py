@@ -116,6 +116,20 @@ def test_tensor_inventory_and_plan_without_a_device():
     assert plan["total_bytes"] > 0 and plan["slots"] == 3
 
 
+def test_the_benchmark_configuration_is_a_valid_model():
+    import bench
+    from mdma_b200.config import load_config
+    from mdma_b200.ops_tensor import attention_supported, talking_attention_mma_warps
+    for width, layers in ((1024, 4), (2048, 6), (4096, 3)):
+        arch, c = load_config(bench.fizadra_config(width, layers, 32000))
+        spec = arch.describe(c)
+        assert len(spec.schedule) == layers and all(e.cache in (None, n - 2) for n, e in enumerate(spec.schedule))
+        latent = c.layers[0].mixer
+        assert attention_supported(latent.heads, 1, latent.kv_rank + latent.rot_dim)       # the tensor-core kernels take it
+        mixed = c.layers[1].mixer
+        assert talking_attention_mma_warps(mixed.heads, mixed.kv_heads, mixed.dim, mixed.vdim) >= 2
+
+
 def test_the_plain_statement_notices_each_mechanism():
     W = {n: t.double() for n, t in make_tensors(CFG_A, 3).items()}
     ids = ids_of(CFG_A, 40, 1)
